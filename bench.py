@@ -1,0 +1,384 @@
+"""Benchmark of the sparse-MLA decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload cfg2|target] [--extras]
+
+One "step" is one sparse decode call (decode kernel + split-KV combine) over a
+batch of synthetic requests: batch 16, h_q 64, d_qk 576 / d_v 512, 32 768-token
+contexts in the 644-byte FP8 + UE8M0 + BF16-RoPE paged cache behind a random
+page table, top-k 2048 (configs[1] of BASELINE.json; `--workload target` runs
+the batch-64 variant).  The metric is achieved HBM GB/s = algorithmic bytes per
+call / time per call.  With N GPUs every rank decodes its own batch of 16 from
+its own cache (request-parallel, no collective): weak scaling.
+
+The timed loop rotates through 16 independent top-k index sets, so the rows
+gathered between two uses of the same set (16 x ~21 MB) exceed the 126 MB L2.
+
+The JSON line carries: `value` (inputs resident in HBM), `roofline` (decode
+kernel alone against the measured copy bandwidth), `e2e` (same metric through
+the public operator with q / indices in pinned host memory copied in and out /
+lse copied back every step; the KV cache is serving state and stays on the
+device), `cpu_baseline` (the CPU oracle, a port of the reference's torch path,
+on the host cores) and the SM clocks sampled during the timed loop.
+
+`--impl reference` times that CPU path alone (rank 0 only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "deepseek-v4-flash-sm120_b200")
+for _p in (ROOT, PKG):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+N_INDEX_SETS = 16
+METRIC = "sparse_decode_achieved_hbm_bandwidth"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    except Exception:  # noqa: BLE001
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a
+    timed region runs (read-only query)."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:  # noqa: BLE001
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:  # noqa: BLE001
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+                for n, v in zip(names, r[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:  # noqa: BLE001
+                continue
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def workload_params(name: str):
+    if name == "cfg2":
+        return dict(b=16, h_q=64, ctx=32768, topk=2048), "configs[1]: decode b=16 h_q=64 ctx=32768 topk=2048, 644-B FP8 paged KV"
+    if name == "target":
+        return dict(b=64, h_q=64, ctx=32768, topk=2048), "north_star target: decode b=64 h_q=64 ctx=32768 topk=2048, 644-B FP8 paged KV"
+    if name == "cfg2_tp16":
+        return dict(b=16, h_q=16, ctx=32768, topk=2048), "configs[1] as one TP shard: h_q=16"
+    raise SystemExit(f"unknown workload {name}")
+
+
+# ----------------------------------------------------------------------------
+# CPU path (the oracle): used by --impl reference and by the cpu_baseline leg.
+# ----------------------------------------------------------------------------
+def time_cpu_oracle(q, kv4, idx, sm_scale, steps: int, warmup: int):
+    from oracle import sparse_mla as O           # CPU baseline leg only
+    layout = O.V32 if kv4.size(3) == 644 else O.MODEL1
+    pages = kv4.view(kv4.size(0), -1)
+    for _ in range(warmup):
+        O.sparse_decode(q, pages, idx, None, None, sm_scale, kv4.size(1), layout)
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        O.sparse_decode(q, pages, idx, None, None, sm_scale, kv4.size(1), layout)
+        times.append(time.perf_counter() - t0)
+    return times
+
+
+def run_reference(args):
+    """The reference's CPU torch path (ported in oracle/), all host threads."""
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    from deepseek_v4_kernel import workloads as W
+    from oracle import sparse_mla as O
+
+    def cpu_quantize(k_nope, k_rope, slots, kv):
+        layout = O.V32 if kv.size(3) == 644 else O.MODEL1
+        body, scales = O.quantize_rows(k_nope, k_rope, layout)
+        nrb = layout.nope_rope_bytes
+        nb, P = kv.size(0), kv.size(1)
+        arena = kv.view(nb, -1)
+        p0 = int(slots[0]) // P                 # fill_cache hands over whole pages in order
+        n_pages = k_nope.size(0) // P
+        arena[p0:p0 + n_pages, : P * nrb] = body.view(n_pages, P * nrb)
+        arena[p0:p0 + n_pages, P * nrb: P * layout.bytes_per_token] = \
+            scales.view(n_pages, P * layout.scale_slots)
+
+    params, desc = workload_params(args.workload)
+    wl = W.config2(torch.device("cpu"), cpu_quantize, n_index_sets=1, **params)
+    steps = max(1, min(args.steps, 8))
+    times = time_cpu_oracle(wl.q, wl.kv, wl.indices[0], wl.sm_scale, steps, min(args.warmup, 1))
+    t = statistics.mean(times)
+    value = wl.algorithmic_bytes() / t / 1e9
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1),
+        "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": desc, "layout": "V32 (576/512, 644 B/token)",
+                   "note": "CPU torch port of the reference's tests/reference.py decode path; "
+                           "it dequantises the whole cache every call, as the reference does"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"{steps} full calls of the workload"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------
+# GPU path
+# ----------------------------------------------------------------------------
+def run_ours(args):
+    rank, world, local = dist_env()
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    from deepseek_v4_kernel import cuda as K
+    from deepseek_v4_kernel import ops
+    from deepseek_v4_kernel import workloads as W
+
+    params, desc = workload_params(args.workload)
+    wl = W.config2(dev, ops.kv_store, n_index_sets=N_INDEX_SETS, seed=rank, **params)
+    stream = torch.cuda.current_stream(dev)
+    call = K.DecodeCall(wl.q, wl.kv, wl.indices[0], wl.sm_scale)
+    alg_bytes = [wl.algorithmic_bytes(i) for i in range(N_INDEX_SETS)]
+    mean_bytes = sum(alg_bytes) / len(alg_bytes)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- (1) inputs resident in HBM: K whole calls ----------------------------------
+    def step(i):
+        call.set_indices(wl.indices[i % N_INDEX_SETS])
+        call.decode(stream.cuda_stream, with_combine=True)
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        ev0.record(stream)
+        for i in range(args.steps):
+            step(i)
+        ev1.record(stream)
+        barrier()
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    ms_per_step = ms_total / args.steps
+    value = world * mean_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- (2) decode kernel alone, per launch (events between the two kernels) -------
+    n_k = min(args.steps, 64)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+           for _ in range(n_k)]
+    for i in range(n_k):
+        call.set_indices(wl.indices[i % N_INDEX_SETS])
+        evs[i][0].record(stream)
+        call.decode(stream.cuda_stream, with_combine=False)
+        evs[i][1].record(stream)
+        call.combine(stream.cuda_stream)
+    torch.cuda.synchronize(dev)
+    k_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+    peak, peak_src = measured_peaks()
+    achieved = mean_bytes / (k_ms * 1e-3) / 1e9
+
+    # ---- (3) end to end through the public operator, host buffers -------------------
+    q_host = wl.q.cpu().pin_memory()
+    idx_host = [t.cpu().pin_memory() for t in wl.indices]
+    out_host = torch.empty((params["b"], 1, params["h_q"], 512), dtype=torch.bfloat16).pin_memory()
+    lse_host = torch.empty((params["b"], params["h_q"], 1), dtype=torch.float32).pin_memory()
+    q_dev = torch.empty_like(wl.q)
+    idx_dev = torch.empty_like(wl.indices[0])
+
+    def e2e_step(i):
+        q_dev.copy_(q_host, non_blocking=True)
+        idx_dev.copy_(idx_host[i % N_INDEX_SETS], non_blocking=True)
+        out, lse, _, _ = ops.sparse_decode_fwd(q_dev, wl.kv, idx_dev, None, None, None, None, None,
+                                               None, None, 512, wl.sm_scale)
+        out_host.copy_(out, non_blocking=True)
+        lse_host.copy_(lse, non_blocking=True)
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(args.steps):
+        e2e_step(i)
+    e1.record(stream)
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    e2e_value = world * mean_bytes / (e2e_ms * 1e-3) / 1e9
+    h2d = q_host.numel() * 2 + idx_host[0].numel() * 4
+    d2h = out_host.numel() * 2 + lse_host.numel() * 4
+
+    # ---- (4) CPU baseline (rank 0, single-GPU run only) -----------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        n_cpu = 2
+        times = time_cpu_oracle(wl.q.cpu(), wl.kv.cpu(), wl.indices[0].cpu(), wl.sm_scale, n_cpu, 1)
+        cpu = {"value": alg_bytes[0] / statistics.mean(times) / 1e9, "unit": "GB/s",
+               "cores": torch.get_num_threads(), "kind": "port",
+               "sample": f"{n_cpu} full calls of the same workload after 1 warm-up "
+                         f"({statistics.mean(times):.2f} s per call)"}
+
+    extras = {}
+    if args.extras and rank == 0:
+        extras = run_extras(dev, K, ops, W, stream)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "us_per_call": ms_per_step * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": desc, "per_gpu_batch": params["b"], "n_splits": call.n_splits,
+                       "kv_pool_mb": wl.kv.numel() / 1e6,
+                       "l2_policy": f"rotates {N_INDEX_SETS} index sets (~{N_INDEX_SETS * wl.kv_gather_bytes() / 1e6:.0f} MB of distinct rows) so inputs exceed L2",
+                       "parallelism": f"request-parallel x{world}, no collective"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "kernel": "sparse decode (gather+dequant+QK^T+softmax+PV)",
+                         "kernel_us": k_ms * 1e3, "algorithmic_bytes_per_launch": mean_bytes,
+                         "kv_gather_gbs": wl.kv_gather_bytes() / (k_ms * 1e-3) / 1e9,
+                         "tflops": wl.flops() / (k_ms * 1e-3) / 1e12},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "gpu_launches": args.steps * call.launches_per_call,
+            "clocks": clocks.summary(),
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        if extras:
+            line["extras"] = extras
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_extras(dev, K, ops, W, stream):
+    """Secondary measurements (opt-in): the batch-64 target, one TP shard
+    (h_q = 16), the forced-128-split combine and the KV store kernel."""
+    out = {}
+
+    def time_calls(fn, n=50, warm=5):
+        for i in range(warm):
+            fn(i)
+        torch.cuda.synchronize(dev)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for i in range(n):
+            fn(i)
+        b.record(stream)
+        torch.cuda.synchronize(dev)
+        return a.elapsed_time(b) / n
+
+    peak, _ = measured_peaks()
+    for name in ("target", "cfg2_tp16"):
+        params, _ = workload_params(name)
+        wl = W.config2(dev, ops.kv_store, n_index_sets=4 if name == "target" else 16, **params)
+        call = K.DecodeCall(wl.q, wl.kv, wl.indices[0], wl.sm_scale)
+        ns = len(wl.indices)
+
+        def fn(i, call=call, wl=wl, ns=ns):
+            call.set_indices(wl.indices[i % ns])
+            call.decode(stream.cuda_stream)
+        ms = time_calls(fn)
+        gbs = wl.algorithmic_bytes() / (ms * 1e-3) / 1e9
+        out[name] = {"us_per_call": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peak,
+                     "n_splits": call.n_splits}
+        del wl, call
+        torch.cuda.empty_cache()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2")
+    ap.add_argument("--extras", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

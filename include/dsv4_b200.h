@@ -1,0 +1,225 @@
+/*
+ * dsv4_b200.h — C ABI of the B200 (sm_100a) sparse-MLA attention library.
+ *
+ * Every entry point takes plain device pointers, sizes and element strides; no
+ * framework types cross this boundary.  Nothing here allocates, frees, retains
+ * or synchronises unless a comment says so: the caller owns inputs, outputs and
+ * scratch, and work is queued on the CUDA stream passed in.  Every function
+ * returns DSV4_OK or a DSV4_ERR_* code (never aborts the process);
+ * dsv4_strerror() turns a code into text.
+ *
+ * Citations name the interface of the reference project
+ * (ambientlight/deepseek-v4-flash-sm120) that the entry point stands in for.
+ */
+#ifndef DSV4_B200_H_
+#define DSV4_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DSV4_ABI_VERSION 1
+
+enum Dsv4Status {
+  DSV4_OK = 0,
+  DSV4_ERR_NULL = 1,        /* a required pointer is null                      */
+  DSV4_ERR_SHAPE = 2,       /* a size is out of the supported range            */
+  DSV4_ERR_LAYOUT = 3,      /* d_qk / KV layout / page stride do not agree     */
+  DSV4_ERR_ALIGN = 4,       /* a pointer or stride breaks an alignment rule    */
+  DSV4_ERR_ARCH = 5,        /* the current device is not sm_100                */
+  DSV4_ERR_CUDA = 6,        /* a CUDA runtime call failed (see dsv4_last_cuda_error) */
+  DSV4_ERR_SCRATCH = 7,     /* n_splits > 1 but scratch pointers are null      */
+  DSV4_ERR_UNSUPPORTED = 8  /* valid request that this build does not implement */
+};
+
+/* KV-cache token layouts.  A page of P tokens is two sections:
+ *   [P x (d_nope FP8 e4m3 bytes + 64 BF16 RoPE values)] [P x scale_slots UE8M0 bytes]
+ * MODEL1: d_nope 448, one scale per 64 values, 7 scales + 1 pad  -> 576 + 8 = 584 B/token
+ *         (reference: tests/reference.py:7-14, csrc/sm120/decode/sparse_decode_kernel.cuh:27-39)
+ * V32   : d_nope 512, one scale per 128 values, 4 scales         -> 640 + 4 = 644 B/token
+ *         (reference: csrc/common/params.h:12-15 names it; the benchmark configs use it)
+ * BF16  : flat rows of d_qk BF16 values, no paging (prefill workspace,
+ *         reference: csrc/common/params.h:99-102)                                      */
+enum Dsv4KvFormat { DSV4_KV_BF16 = 0, DSV4_KV_MODEL1 = 1, DSV4_KV_V32 = 2 };
+
+enum Dsv4Flags {
+  /* Decode only: treat an index < 0 or >= num_tokens as masked (-inf) the way
+   * upstream FlashMLA does.  Default (flag clear) follows the reference oracle:
+   * such an index gathers a zero row that still scores logit 0
+   * (tests/reference.py:110-119).                                                      */
+  DSV4_FLAG_MASK_INVALID = 1,
+  /* Run the plain CUDA-core kernels instead of the tcgen05 ones (debug aid).           */
+  DSV4_FLAG_IMPL_SIMPLE = 2,
+  /* Decode with n_splits > 1: stop after writing the partials; the caller runs
+   * dsv4_split_combine itself (lets a benchmark time the two kernels apart).           */
+  DSV4_FLAG_NO_COMBINE = 4
+};
+
+/* ---------------------------------------------------------------------------
+ * Sparse decode: replaces dsv4_kernel::sparse_decode_fwd
+ * (csrc/api/sparse_decode.cpp:27-220) and its parameter block
+ * SparseAttnDecodeParams (csrc/common/params.h:34-97).
+ *
+ * For request r = (b_idx, s_idx) the kernel attends q[r] over the rows named by
+ * indices[r, 0:len) of the paged cache (then extra_indices[r, 0:extra_len) of
+ * the extra cache when given), V being the first 512 columns of the dequantised
+ * row, and writes out[r] (BF16) and lse[r] (fp32, natural log, sink-merged).
+ * len = clamp(topk_length[b_idx], 1, topk) when topk_length is given, else topk.
+ * Strides are in elements of the tensor's own type, except stride_kv_block and
+ * stride_extra_kv_block which are in BYTES.  All inner dimensions are dense.
+ * q rows and KV pages must be 16-byte aligned.
+ *
+ * When n_splits > 1 each request's list is cut into n_splits ranges that write
+ * locally normalised fp32 partials to o_accum [n_splits, b*s_q, h_q, 512] and
+ * lse_accum [n_splits, b*s_q, h_q]; the same call then runs the combine step.
+ * ------------------------------------------------------------------------- */
+typedef struct Dsv4DecodeArgs {
+  int32_t b, s_q, h_q, d_qk, d_v, topk;
+  int32_t kv_format;            /* DSV4_KV_MODEL1 or DSV4_KV_V32                 */
+  int32_t num_blocks, page_block_size;
+  int32_t extra_num_blocks, extra_page_block_size, extra_topk;
+  int32_t n_splits;             /* >= 1; see dsv4_plan_splits                    */
+  int32_t flags;                /* Dsv4Flags                                     */
+  float sm_scale;
+  int32_t _pad0;
+
+  const void* q;                /* BF16 [b, s_q, h_q, d_qk]                      */
+  const void* kv;               /* bytes [num_blocks, stride_kv_block]           */
+  const int32_t* indices;       /* [b, s_q, topk]                                */
+  const int32_t* topk_length;   /* [b] or null                                   */
+  const float* attn_sink;       /* [h_q] or null                                 */
+  const void* extra_kv;         /* or null                                       */
+  const int32_t* extra_indices; /* [b, s_q, extra_topk] or null                  */
+  const int32_t* extra_topk_length; /* [b] or null                               */
+
+  void* out;                    /* BF16 [b, s_q, h_q, 512]                       */
+  float* lse;                   /* fp32, addressed with the three lse strides    */
+  float* o_accum;               /* scratch, n_splits > 1                         */
+  float* lse_accum;             /* scratch, n_splits > 1                         */
+
+  int64_t stride_q_b, stride_q_s, stride_q_h;
+  int64_t stride_kv_block, stride_extra_kv_block;
+  int64_t stride_indices_b, stride_indices_s;
+  int64_t stride_extra_indices_b, stride_extra_indices_s;
+  int64_t stride_o_b, stride_o_s, stride_o_h;
+  int64_t stride_lse_b, stride_lse_s, stride_lse_h;
+} Dsv4DecodeArgs;
+
+int dsv4_sparse_decode(const Dsv4DecodeArgs* args, void* cuda_stream);
+
+/* Split count for a decode call: a pure function of shapes and the SM count, so
+ * it is stable under CUDA-graph capture.  Stands in for the heuristic at
+ * csrc/api/sparse_decode.cpp:147-171 (the policy differs: it is sized for one
+ * CTA per SM that owns up to 64 heads and walks 128-row tiles).                  */
+int dsv4_plan_splits(int b, int s_q, int h_q, int topk, int extra_topk, int num_sms);
+
+/* ---------------------------------------------------------------------------
+ * Split-KV combine alone: replaces dsv4_split_kv_combine
+ * (csrc/sm120/decode/split_kv_combine.cuh:23-110).
+ * o_accum fp32 [n_splits, n_rows, h_q, 512] and lse_accum fp32
+ * [n_splits, n_rows, h_q], both dense; row r of the output lives at
+ * out + (r / s_q) * stride_o_b + (r % s_q) * stride_o_s  (likewise lse).
+ * ------------------------------------------------------------------------- */
+typedef struct Dsv4CombineArgs {
+  int32_t n_rows, s_q, h_q, n_splits;
+  const float* o_accum;
+  const float* lse_accum;
+  const float* attn_sink;       /* [h_q] or null                                 */
+  void* out;                    /* BF16                                          */
+  float* lse;
+  int64_t stride_o_b, stride_o_s, stride_o_h;
+  int64_t stride_lse_b, stride_lse_s, stride_lse_h;
+} Dsv4CombineArgs;
+
+int dsv4_split_combine(const Dsv4CombineArgs* args, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------
+ * Sparse prefill: replaces dsv4_kernel::sparse_prefill_fwd
+ * (csrc/api/sparse_prefill.cpp:27-136, SparseAttnPrefillParams
+ * csrc/common/params.h:103-135).  kv_format DSV4_KV_BF16 is the reference's
+ * flat workspace kv[s_kv, d_qk]; MODEL1 / V32 read the FP8 paged cache directly
+ * (s_kv = num_blocks * page_block_size).  An index < 0, >= s_kv, or at a
+ * position >= topk_length[i] is masked.  Outputs: out BF16 [s_q, h_q, 512],
+ * max_logits and lse fp32 [s_q, h_q] (natural log; lse excludes the sink; a row
+ * with nothing to attend to gives out 0, max_logits -inf, lse +inf).
+ * ------------------------------------------------------------------------- */
+typedef struct Dsv4PrefillArgs {
+  int32_t s_q, s_kv, h_q, d_qk, d_v, topk;
+  int32_t kv_format;
+  int32_t num_blocks, page_block_size;
+  int32_t flags;
+  float sm_scale;
+  int32_t _pad0;
+
+  const void* q;                /* BF16 [s_q, h_q, d_qk]                         */
+  const void* kv;               /* BF16 [s_kv, d_qk] or paged bytes              */
+  const int32_t* indices;       /* [s_q, topk]                                   */
+  const float* attn_sink;       /* [h_q] or null                                 */
+  const int32_t* topk_length;   /* [s_q] or null                                 */
+  void* out;
+  float* max_logits;
+  float* lse;
+
+  int64_t stride_q_s, stride_q_h;
+  int64_t stride_kv_row;        /* elements (BF16) or bytes per page (paged)     */
+  int64_t stride_indices_s;
+  int64_t stride_o_s, stride_o_h;
+  int64_t stride_ml_s, stride_lse_s;
+} Dsv4PrefillArgs;
+
+int dsv4_sparse_prefill(const Dsv4PrefillArgs* args, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------
+ * KV store / quantise.  The reference has no such kernel: its cache is written
+ * by the serving framework (tests/reference.py:48-49 names quant_k_cache_v4).
+ * Per token i with slot s = slots[i] >= 0 (page s / P, row s % P): for each
+ * tile of quant_tile latent values e = ceil(log2(max(amax, 1e-4) / 448)), scale
+ * byte e + 127, fp8 = saturating round-to-nearest-even e4m3 of x * 2^-e; RoPE
+ * copied as BF16; unused scale slots written as zero.
+ * ------------------------------------------------------------------------- */
+typedef struct Dsv4StoreArgs {
+  int32_t n_tokens, kv_format, num_blocks, page_block_size;
+  const void* k_nope;           /* BF16 [n_tokens, d_nope]                       */
+  const void* k_rope;           /* BF16 [n_tokens, 64]                           */
+  const int64_t* slots;         /* [n_tokens]; negative = skip                   */
+  void* kv;                     /* paged cache bytes                             */
+  int64_t stride_nope, stride_rope, stride_kv_block;   /* elements, elements, bytes */
+} Dsv4StoreArgs;
+
+int dsv4_kv_store(const Dsv4StoreArgs* args, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------
+ * Gather + dequantise only (checks that row selection and FP8 -> BF16 are
+ * bit-exact): rows[i] = dequantised d_qk BF16 values of token indices[i], or
+ * zeros for an index outside [0, num_blocks * page_block_size).  Uses the same
+ * device routine as the decode kernel when method == 0 (packed-BF16 multiply);
+ * method == 1 converts through fp32 instead (reference: load_kv_chunk,
+ * csrc/sm120/decode/sparse_decode_kernel.cuh:101-167).
+ * ------------------------------------------------------------------------- */
+int dsv4_gather_dequant(const void* kv, int64_t stride_kv_block, int32_t kv_format,
+                        int32_t num_blocks, int32_t page_block_size,
+                        const int32_t* indices, int32_t n, void* rows_bf16,
+                        int32_t method, void* cuda_stream);
+
+/* Device facts, cached per device after the first call (reference: Arch,
+ * csrc/common/params.h:138-156, which queries on every call).                         */
+int dsv4_device_info(int device, int* major, int* minor, int* num_sms);
+
+/* Text for a status code; the last CUDA error string seen by this thread.             */
+const char* dsv4_strerror(int status);
+const char* dsv4_last_cuda_error(void);
+int dsv4_abi_version(void);
+
+/* Tensor-core self-test used by the test-suite: one 128 x n x k BF16 product
+ * through tcgen05.mma with the shared-memory operand arrangement the attention
+ * kernel uses (mode 0: both operands K-major; mode 1: A and B MN-major).
+ * a, b, d are device pointers (BF16, BF16, fp32 row-major [128, n]).                   */
+int dsv4_umma_selftest(int mode, int n, int k, const void* a, const void* b, float* d,
+                       int32_t* status, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSV4_B200_H_ */

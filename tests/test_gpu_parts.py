@@ -1,0 +1,107 @@
+"""GPU checks of the pieces around the attention kernel: FP8 gather/dequantise
+(bit-exact), the KV store/quantise kernel (bit-exact), the split-KV combine and
+the tensor-core descriptor self-test."""
+import pytest
+import torch
+
+from oracle import sparse_mla as O
+from util import max_rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    assert torch.cuda.is_available() and torch.cuda.get_device_capability(0)[0] == 10
+    from deepseek_v4_kernel import cuda as K
+    return K
+
+
+@pytest.mark.parametrize("layout", [O.MODEL1, O.V32], ids=["model1", "v32"])
+@pytest.mark.parametrize("method", [0, 1], ids=["packed_bf16", "via_fp32"])
+def test_gather_dequant_bit_exact_all_bytes(K, layout, method):
+    """Every e4m3 byte (NaN codes excepted) under a spread of scale bytes, and
+    row selection through the page table arithmetic."""
+    scale_bytes = [0, 1, 2, 100, 118, 125, 126, 127, 128, 133, 134, 135, 140, 200, 254]
+    n = 64 * len(scale_bytes)
+    body = torch.zeros(n, layout.nope_rope_bytes, dtype=torch.uint8)
+    vals = torch.arange(256, dtype=torch.int16)
+    vals = vals[(vals & 0x7f) != 0x7f].to(torch.uint8)                  # drop the two NaN codes
+    gen = torch.Generator().manual_seed(0)
+    for r in range(n):
+        body[r, :layout.d_nope] = vals[torch.randint(0, vals.numel(), (layout.d_nope,), generator=gen)]
+        body[r, :254] = vals                                             # every code in every row
+    body[:, layout.d_nope:] = torch.randint(0, 256, (n, 128), generator=gen, dtype=torch.uint8)
+    scales = torch.zeros(n, layout.scale_slots, dtype=torch.uint8)
+    for i, s in enumerate(scale_bytes):
+        scales[i * 64:(i + 1) * 64, :layout.scale_active] = s
+    scales[:, 1:layout.scale_active] = torch.tensor(scale_bytes)[torch.randint(
+        0, len(scale_bytes), (n, layout.scale_active - 1), generator=gen)].to(torch.uint8)
+    nb = n // 64
+    nrb = layout.nope_rope_bytes
+    pages = torch.cat([body.view(nb, 64 * nrb), scales.view(nb, 64 * layout.scale_slots)], 1).contiguous()
+    dense = O.pages_to_bf16(pages, 64, layout)
+    idx = torch.cat([torch.randperm(n, generator=gen), torch.tensor([-1, n, n + 5])]).int()
+    want = torch.zeros(idx.numel(), layout.d_qk, dtype=torch.bfloat16)
+    ok = (idx >= 0) & (idx < n)
+    want[ok] = dense[idx[ok].long()]
+    kv4 = pages.cuda().view(nb, 64, 1, layout.bytes_per_token)
+    got = K.gather_dequant(kv4, idx.cuda(), method).cpu()
+    # RoPE bytes are arbitrary bit patterns (may be NaN): compare as integers
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.parametrize("layout", [O.MODEL1, O.V32], ids=["model1", "v32"])
+def test_kv_store_bit_exact(K, layout):
+    gen = torch.Generator().manual_seed(2)
+    n, nb = 300, 6
+    mag = torch.logspace(-5, 3, n).unsqueeze(1)
+    k_nope = (torch.randn(n, layout.d_nope, generator=gen) * mag).bfloat16()
+    k_nope[5] = 0
+    k_nope[6, :layout.quant_tile] = 448.0                     # amax exactly on a power-of-two edge
+    k_nope[7, :layout.quant_tile] = 224.0
+    k_rope = torch.randn(n, 64, generator=gen).bfloat16()
+    slots = torch.randperm(nb * 64, generator=gen)[:n].long()
+    slots[11] = -1
+    want = torch.full((nb, layout.page_bytes(64)), 0xAB, dtype=torch.uint8)
+    body, scales = O.quantize_rows(k_nope, k_rope, layout)
+    O.store_rows(want, 64, layout, slots, body, scales)
+    kv = torch.full((nb, layout.page_bytes(64)), 0xAB, dtype=torch.uint8, device="cuda")
+    kv4 = kv.view(nb, 64, 1, layout.bytes_per_token)
+    K.kv_store(k_nope.cuda(), k_rope.cuda(), slots.cuda(), kv4)
+    assert torch.equal(kv.cpu(), want)
+    # store -> gather returns the input rounded through FP8 with the tile scale
+    back = K.gather_dequant(kv4, slots.clamp(min=0).int().cuda()).cpu()
+    assert torch.equal(back[:, layout.d_nope:][slots >= 0], k_rope[slots >= 0])
+
+
+@pytest.mark.parametrize("n_splits,h_q", [(2, 16), (5, 64), (128, 64), (256, 8)])
+@pytest.mark.parametrize("with_sink", [False, True])
+def test_combine_matches_oracle(K, n_splits, h_q, with_sink):
+    gen = torch.Generator().manual_seed(n_splits)
+    rows = 3
+    o = torch.randn(n_splits, rows, h_q, 512, generator=gen)
+    l = torch.randn(n_splits, rows, h_q, generator=gen) * 3
+    l[torch.rand(n_splits, rows, h_q, generator=gen) < 0.2] = float("-inf")
+    l[:, 1, 2] = float("-inf")                                 # a fully empty row/head
+    sink = torch.randn(h_q, generator=gen) if with_sink else None
+    out_ref, lse_ref = O.combine_splits(o, l, sink)
+    out, lse = K.split_combine(o.cuda(), l.cuda(), None if sink is None else sink.cuda())
+    torch.testing.assert_close(lse.cpu(), lse_ref, atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(out.cpu().float(), out_ref.float(), atol=1e-2, rtol=1e-2)
+    assert (out.cpu()[1, 2] == 0).all()
+
+
+@pytest.mark.parametrize("mode,n,k", [(0, 64, 64), (0, 64, 256), (0, 16, 128), (0, 32, 192),
+                                      (1, 64, 64), (1, 64, 256), (1, 32, 128), (1, 16, 128)])
+def test_umma_descriptor_selftest(K, mode, n, k):
+    gen = torch.Generator().manual_seed(mode * 100 + n + k)
+    a = torch.randn(128, k, generator=gen).bfloat16()
+    b = torch.randn(n, k, generator=gen).bfloat16()
+    want = a.float() @ b.float().t()
+    if mode == 0:
+        d, status = K.umma_selftest(0, a.cuda(), b.cuda())
+    else:
+        d, status = K.umma_selftest(1, a.t().contiguous().cuda(), b.t().contiguous().cuda())
+    assert status == 0, "the MMA never signalled its barrier"
+    torch.testing.assert_close(d.cpu(), want, atol=1e-3, rtol=1e-3)
