@@ -298,6 +298,15 @@ int dsv4_gather_dequant(const void* kv, int64_t stride_kv_block, int32_t kv_form
   return e ? cuda_fail(e) : DSV4_OK;
 }
 
+int dsv4_device_status(int32_t* status_out, int reset) {
+  if (!status_out) return DSV4_ERR_NULL;
+  int v = 0;
+  cudaError_t e = dsv4::read_attn_error(&v, reset != 0);
+  if (e) return cuda_fail(e);
+  *status_out = v;
+  return DSV4_OK;
+}
+
 int dsv4_umma_selftest(int mode, int n, int k, const void* a, const void* b, float* d,
                        int32_t* status, void* stream) {
   if (!a || !b || !d || !status) return DSV4_ERR_NULL;

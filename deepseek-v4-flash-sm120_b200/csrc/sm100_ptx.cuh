@@ -23,21 +23,25 @@ __device__ __forceinline__ void mbar_init_fence() {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+// Non-blocking probe of a phase.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls and returns false, so that a
-// protocol error ends the kernel with a status code instead of a hang.
+// Bounded wait: polls, backing off to short sleeps, and gives up after `limit`
+// polls (some tens of milliseconds) returning false, so that a protocol error
+// ends the kernel with a status code instead of a hang.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          uint32_t limit = (1u << 22)) {
-  for (uint32_t i = 0; i < limit; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
+                                          uint32_t limit = (1u << 20)) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if (i > 64) __nanosleep(32);
+  }
   return false;
 }
 

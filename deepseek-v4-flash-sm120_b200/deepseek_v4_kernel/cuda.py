@@ -295,6 +295,13 @@ def split_combine(o_accum, lse_accum, attn_sink=None, s_q: int = 1):
     return out, lse
 
 
+def device_status(reset: bool = True) -> int:
+    """Health word of the tensor-core kernels on the current device (synchronises)."""
+    v = C.c_int32(0)
+    N.check(N.lib.dsv4_device_status(C.byref(v), 1 if reset else 0), "dsv4_device_status")
+    return v.value
+
+
 def umma_selftest(mode: int, a: torch.Tensor, b: torch.Tensor) -> Tuple[torch.Tensor, int]:
     """Run the tensor-core self-test; see dsv4_umma_selftest in the C header."""
     if mode == 0:

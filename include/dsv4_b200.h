@@ -207,6 +207,13 @@ int dsv4_gather_dequant(const void* kv, int64_t stride_kv_block, int32_t kv_form
  * csrc/common/params.h:138-156, which queries on every call).                         */
 int dsv4_device_info(int device, int* major, int* minor, int* num_sms);
 
+/* Device-side health word of the tensor-core attention kernels on the current
+ * device: 0, or the code of the first bounded wait that gave up (the kernel then
+ * returned early and its outputs are not valid).  Copies from the device, so it
+ * SYNCHRONISES with work already queued; reset != 0 clears the word.  A serving
+ * loop need not call it; the tests do after every launch.                             */
+int dsv4_device_status(int32_t* status_out, int reset);
+
 /* Text for a status code; the last CUDA error string seen by this thread.             */
 const char* dsv4_strerror(int status);
 const char* dsv4_last_cuda_error(void);

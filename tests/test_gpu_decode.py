@@ -27,6 +27,8 @@ def cuda_mod():
 
 def check(out, lse, out_ref, lse_ref):
     """lse arrives as [b, h_q, s_q]; the oracle returns [b, s_q, h_q]."""
+    from deepseek_v4_kernel import cuda as K
+    assert K.device_status() == 0, "a bounded wait inside the kernel gave up"
     out, lse = out.cpu(), lse.cpu().transpose(1, 2)
     torch.testing.assert_close(lse, lse_ref, atol=1e-3, rtol=1e-3)
     torch.testing.assert_close(out.float(), out_ref.float(), atol=5e-3, rtol=5e-3)
