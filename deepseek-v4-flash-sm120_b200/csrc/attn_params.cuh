@@ -16,6 +16,7 @@ struct AttnParams {
   int h_q, topk, extra_topk, n_splits, flags, mode;
   int page_block, n_tok;              // main cache: tokens per page, total tokens (s_kv)
   int extra_page_block, extra_n_tok;
+  int page_shift, extra_page_shift;   // log2 of the page size, or -1 when it is not a power of two
   float sm_scale;
 
   const __nv_bfloat16* q;
@@ -39,6 +40,7 @@ struct AttnParams {
   int64_t stride_o_b, stride_o_s, stride_o_h;
   int64_t stride_lse_b, stride_lse_s, stride_lse_h;
   int64_t stride_ml_b;                          // max_logits row stride (prefill)
+  long long* prof;                              // optional timeline buffer (debug), or null
 };
 
 // Effective list lengths of request `req`: `len` entries of the main list then

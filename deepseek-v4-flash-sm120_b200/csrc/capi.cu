@@ -65,6 +65,15 @@ int check_paged(int kv_format, int d_qk, int page_block, int64_t stride_block, c
   return DSV4_OK;
 }
 
+long long* g_timeline = nullptr;
+
+int log2_or_minus1(int v) {
+  if (v <= 0 || (v & (v - 1))) return -1;
+  int s = 0;
+  while ((1 << s) < v) ++s;
+  return s;
+}
+
 bool want_simple(int flags) {
   if (flags & DSV4_FLAG_IMPL_SIMPLE) return true;
   const char* e = std::getenv("DSV4_IMPL");
@@ -175,6 +184,8 @@ int dsv4_sparse_decode(const Dsv4DecodeArgs* a, void* stream) {
   p.n_tok = a->num_blocks * a->page_block_size;
   p.extra_page_block = a->extra_kv ? a->extra_page_block_size : 1;
   p.extra_n_tok = a->extra_kv ? a->extra_num_blocks * a->extra_page_block_size : 0;
+  p.page_shift = log2_or_minus1(p.page_block);
+  p.extra_page_shift = log2_or_minus1(p.extra_page_block);
   p.sm_scale = a->sm_scale;
   p.q = static_cast<const __nv_bfloat16*>(a->q);
   p.kv = static_cast<const uint8_t*>(a->kv);
@@ -195,6 +206,7 @@ int dsv4_sparse_decode(const Dsv4DecodeArgs* a, void* stream) {
   p.stride_xidx_b = a->stride_extra_indices_b; p.stride_xidx_s = a->stride_extra_indices_s;
   p.stride_o_b = a->stride_o_b; p.stride_o_s = a->stride_o_s; p.stride_o_h = a->stride_o_h;
   p.stride_lse_b = a->stride_lse_b; p.stride_lse_s = a->stride_lse_s; p.stride_lse_h = a->stride_lse_h;
+  p.prof = g_timeline;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
@@ -246,6 +258,8 @@ int dsv4_sparse_prefill(const Dsv4PrefillArgs* a, void* stream) {
   p.page_block = a->kv_format == DSV4_KV_BF16 ? 1 : a->page_block_size;
   p.n_tok = a->kv_format == DSV4_KV_BF16 ? a->s_kv : a->num_blocks * a->page_block_size;
   p.extra_page_block = 1;
+  p.page_shift = log2_or_minus1(p.page_block);
+  p.extra_page_shift = 0;
   p.sm_scale = a->sm_scale;
   p.q = static_cast<const __nv_bfloat16*>(a->q);
   p.kv = static_cast<const uint8_t*>(a->kv);
@@ -261,6 +275,7 @@ int dsv4_sparse_prefill(const Dsv4PrefillArgs* a, void* stream) {
   p.stride_o_b = a->stride_o_s; p.stride_o_h = a->stride_o_h;
   p.stride_lse_b = a->stride_lse_s; p.stride_lse_h = 1;
   p.stride_ml_b = a->stride_ml_s;
+  p.prof = g_timeline;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
@@ -296,6 +311,11 @@ int dsv4_gather_dequant(const void* kv, int64_t stride_kv_block, int32_t kv_form
                                               page_block_size, indices, n, rows_bf16, method,
                                               static_cast<cudaStream_t>(stream));
   return e ? cuda_fail(e) : DSV4_OK;
+}
+
+int dsv4_debug_set_timeline(void* device_buffer) {
+  g_timeline = static_cast<long long*>(device_buffer);
+  return DSV4_OK;
 }
 
 int dsv4_device_status(int32_t* status_out, int reset) {

@@ -33,16 +33,36 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait: polls, backing off to short sleeps, and gives up after `limit`
-// polls (some tens of milliseconds) returning false, so that a protocol error
-// ends the kernel with a status code instead of a hang.
+// Probe that lets the hardware suspend the thread for up to `ns` nanoseconds
+// while the phase is pending (no polling traffic on shared memory meanwhile).
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+  return ok != 0;
+}
+// Bounded wait: non-blocking probes with a short pause in between (an explicit
+// pause keeps the wake-up latency at tens of nanoseconds; a suspending try_wait
+// with a time hint was observed to sleep for the whole hint).  Gives up after
+// `limit` probes (roughly a tenth of a second) and returns false, so that a
+// protocol error ends the kernel with a status code instead of a hang.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          uint32_t limit = (1u << 20)) {
+                                          uint32_t limit = (1u << 21)) {
   for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_test(bar, parity)) return true;
-    if (i > 64) __nanosleep(32);
+    if (i > 8) __nanosleep(20);
   }
   return false;
+}
+// The same for a whole warp: lane 0 waits, the result is broadcast.  Keeps the number
+// of waiters on shared memory at one per warp.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int lane) {
+  uint32_t ok = 1;
+  if (lane == 0) ok = mbar_wait(bar, parity) ? 1u : 0u;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // ---- fences ---------------------------------------------------------------
@@ -84,6 +104,20 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Same, with each descriptor given as its low and high 32-bit words so that stepping
+// the start address costs one 32-bit add.
+__device__ __forceinline__ void umma_bf16_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi,
+                                               uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 // Arrive on an mbarrier once all MMAs issued so far by this thread complete.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {

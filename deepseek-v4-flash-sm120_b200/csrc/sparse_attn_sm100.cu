@@ -13,14 +13,16 @@
 // (contraction over d) for the first product and as MN-major (contraction over
 // tokens) for the second.  With d_qk = 576 the tile (144 KB) and Q (72 KB) leave
 // no room for a second tile or a staging ring, so gathered rows are staged in
-// REGISTERS: each producer warp owns 16 rows of the tile, issues the 16-byte
-// loads of the next tile while the current one is being multiplied, and writes
-// them (dequantised to BF16) as soon as the P.V step that last read those 16
-// rows has retired.  P^T (16 KB) reuses the RoPE block of the tile, which only
+// REGISTERS: each producer warp owns one 64-column block of every tile row,
+// issues the 16-byte loads of the next tile while the current one is being
+// multiplied, and writes each group of 16 rows (dequantised to BF16) as soon as
+// the P.V step that last read those rows has retired.  P^T (16 KB) reuses the RoPE block of the tile, which only
 // Q.K^T reads, when d_qk = 576.
 //
-// Warp roles (13 warps): 0-3 softmax (one thread per tile row = TMEM lane),
-// 4-11 producers (gather + dequantise + swizzled store), 12 MMA issue + TMEM.
+// Warp roles (16 warps x 128 registers fill the register file): 0-7 softmax (a
+// thread owns one tile row = TMEM lane and 32 of the 64 heads), 8-15 producers
+// (gather + dequantise + swizzled store).  Thread 0 also issues the MMAs, which
+// run asynchronously, in between its softmax steps; warp 0 owns TMEM.
 // TMEM columns: [0,64) S^T, [64,320) the four 128-row slices of O^T.
 //
 // Softmax: running per-head reference max with lazy rescaling (O^T is touched
@@ -43,9 +45,9 @@ using namespace ptx;
 
 constexpr int TILE = 128;              // index entries per tile (= MMA M)
 constexpr int HEADS = 64;              // heads per CTA (= MMA N)
-constexpr int SOFTMAX_WARPS = 4, PRODUCER_WARPS = 8;
-constexpr int MMA_WARP = SOFTMAX_WARPS + PRODUCER_WARPS;
-constexpr int THREADS = (MMA_WARP + 1) * 32;          // 416
+constexpr int SOFTMAX_WARPS = 8, PRODUCER_WARPS = 8;
+constexpr int WORK_WARPS = SOFTMAX_WARPS + PRODUCER_WARPS;
+constexpr int THREADS = WORK_WARPS * 32;              // 512 threads x 128 registers = the whole file
 constexpr int KBLOCK_BYTES = TILE * 128;              // [128 tok][64 bf16]
 constexpr int QBLOCK_BYTES = HEADS * 128;
 constexpr uint32_t TMEM_COLS = 512;
@@ -67,11 +69,13 @@ template <int FMT, int DQK> struct Cfg {
 
 struct Ctrl {
   uint64_t k_full, s_full, p_full, o_done;
-  uint64_t kv_free[PRODUCER_WARPS];
+  uint64_t kv_free[8];                 // one per P.V k-step (16 tile rows)
   uint32_t tmem;
   int resc[2];
-  float wred[SOFTMAX_WARPS][HEADS];    // per-warp column partials (max, then sums)
+  int fail;
+  float wred[4][HEADS];                // per-lane-group column partials (max, then sums)
   float mref[HEADS];                   // reference max, log2-scaled units
+  float muse[HEADS];                   // mref with -inf replaced by 0 (exponent offset)
   float mtrue[HEADS];                  // true running max, log2-scaled units
   float alpha[HEADS];                  // rescale factor / final output factor
 };
@@ -116,6 +120,12 @@ __device__ __forceinline__ float warp_col_reduce32(float (&v)[32], int lane) {
   return v[0];
 }
 
+// Debug timeline: SM cycle counter of CTA (0,0,0) into p.prof[slot] when a buffer is set.
+__device__ __forceinline__ void stamp(const AttnParams& p, int slot) {
+  if (p.prof != nullptr && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) p.prof[slot] = clock64();
+}
+constexpr int PROF_TILE0 = 8, PROF_PER_TILE = 8, PROF_MAX_TILES = 15;
+
 struct ListView {
   const int32_t* main_idx;
   const int32_t* extra_idx;
@@ -132,85 +142,136 @@ __device__ __forceinline__ bool list_entry(const AttnParams& p, const ListView& 
 }
 
 // ---------------------------------------------------------------------------
-// Producer: registers for one group of 8 rows (one row per 4 lanes).
+// Producer staging.  A tile is 8 "k-steps" of 16 rows (the rows one P.V MMA
+// step contracts over).  Producer warp pw owns column block pw (64 values) of
+// EVERY row: per k-step lane l holds half a block row (row 16j + l/2, half l&1).
+// So when P.V retires k-step j, all eight warps refill those 16 rows at once,
+// and the refill of the whole tile trails the P.V product by one k-step.
+// The last block (RoPE / columns 512..575) of k-step j is handled by warp j.
 // ---------------------------------------------------------------------------
-template <int FMT, int DQK> struct RowRegs {
+template <int FMT, int DQK> struct Stage {
   using C = Cfg<FMT, DQK>;
-  static constexpr int NVEC = C::PAGED ? C::NOPE_SEGS + 2 : C::NB * 2;
-  uint4 v[NVEC];
-  uint32_t sc[2];
-
-  __device__ __forceinline__ void zero() {
-#pragma unroll
-    for (int i = 0; i < NVEC; ++i) v[i] = make_uint4(0, 0, 0, 0);
-    sc[0] = sc[1] = 0x7f7f7f7fu;
-  }
-
-  // lane quarter qd (0..3) of the row's 4 lanes.
-  __device__ __forceinline__ void load(const AttnParams& p, bool is_main, int idx, int qd) {
-    const uint8_t* kv = is_main ? p.kv : p.extra_kv;
-    const int64_t stride = is_main ? p.stride_kv : p.stride_extra_kv;
-    if constexpr (C::PAGED) {
-      const uint8_t *row, *scl;
-      token_ptrs<FMT>(kv, stride, is_main ? p.page_block : p.extra_page_block, idx, row, scl);
-#pragma unroll
-      for (int i = 0; i < C::NOPE_SEGS; ++i) v[i] = ldg16(row + 64 * i + 16 * qd);
-      v[C::NOPE_SEGS] = ldg16(row + 64 * C::NOPE_SEGS + 16 * qd);
-      v[C::NOPE_SEGS + 1] = ldg16(row + 64 * C::NOPE_SEGS + 64 + 16 * qd);
-      sc[0] = __ldg(reinterpret_cast<const uint32_t*>(scl));
-      if constexpr (KvTraits<FMT>::SLOTS == 8) sc[1] = __ldg(reinterpret_cast<const uint32_t*>(scl) + 1);
-    } else {
-      const uint8_t* row = kv + static_cast<int64_t>(idx) * stride * 2;
-#pragma unroll
-      for (int i = 0; i < C::NB; ++i) {
-        v[2 * i] = ldg16(row + 128 * i + 32 * qd);
-        v[2 * i + 1] = ldg16(row + 128 * i + 32 * qd + 16);
-      }
-    }
-  }
-
-  // Write the row (tile row `row`, row & 7 == r) into the swizzled K tile.
-  __device__ __forceinline__ void store(uint32_t k_base, int row, int r, int qd) const {
-    const uint32_t rbase = k_base + row * 128;
-    if constexpr (C::PAGED) {
-      using T = KvTraits<FMT>;
-#pragma unroll
-      for (int i = 0; i < C::NOPE_SEGS; ++i) {
-        const int tile_no = i * 64 / T::TILE;
-        const uint32_t s = (sc[tile_no >> 2] >> (8 * (tile_no & 3))) & 0xffu;
-        const ScaleMul mul = make_scale_mul(s);
-        uint32_t o[8];
-        dequant4_fast(v[i].x, mul, o[0], o[1]);
-        dequant4_fast(v[i].y, mul, o[2], o[3]);
-        dequant4_fast(v[i].z, mul, o[4], o[5]);
-        dequant4_fast(v[i].w, mul, o[6], o[7]);
-        const uint32_t a = rbase + i * KBLOCK_BYTES;
-        st_shared_v4(a + (((2 * qd) ^ r) << 4), o[0], o[1], o[2], o[3]);
-        st_shared_v4(a + (((2 * qd + 1) ^ r) << 4), o[4], o[5], o[6], o[7]);
-      }
-      const uint32_t a = rbase + C::NOPE_SEGS * KBLOCK_BYTES;          // RoPE block
-      const uint4 x = v[C::NOPE_SEGS], y = v[C::NOPE_SEGS + 1];
-      st_shared_v4(a + ((qd ^ r) << 4), x.x, x.y, x.z, x.w);
-      st_shared_v4(a + (((4 + qd) ^ r) << 4), y.x, y.y, y.z, y.w);
-    } else {
-#pragma unroll
-      for (int i = 0; i < C::NB; ++i) {
-        const uint32_t a = rbase + i * KBLOCK_BYTES;
-        st_shared_v4(a + (((2 * qd) ^ r) << 4), v[2 * i].x, v[2 * i].y, v[2 * i].z, v[2 * i].w);
-        st_shared_v4(a + (((2 * qd + 1) ^ r) << 4), v[2 * i + 1].x, v[2 * i + 1].y, v[2 * i + 1].z,
-                     v[2 * i + 1].w);
-      }
-    }
-  }
+  static constexpr int NV = C::PAGED ? 2 : 4;             // uint4 per lane per k-step
+  static constexpr int PHASES = C::PAGED ? 1 : 2;         // BF16 rows are staged half a tile at a time
+  static constexpr int KS = 8 / PHASES;                   // k-steps held in registers at once
+  static constexpr int MAIN_BLOCKS = C::PAGED ? C::NOPE_SEGS : (DQK == 576 ? 8 : C::NB);
+  static constexpr bool HAS_LAST = C::PAGED || DQK == 576;  // a block beyond MAIN_BLOCKS exists
+  uint4 d[KS][NV];
+  uint32_t sc[KS];
+  uint4 last[4];
 };
 
+// List entry j as (index, which cache) without branching: entries past the end read as -1.
+__device__ __forceinline__ int list_index(const ListView& lv, int j) {
+  const bool in_range = j < lv.end;
+  const bool is_main = j < lv.len;
+  const int32_t* src = is_main ? lv.main_idx + j : lv.extra_idx + (j - lv.len);
+  return in_range ? __ldg(src) : -1;
+}
+
+// Issue the loads of phase `ph` of the tile whose first list entry is j0.  All index
+// loads go out first, then all row loads, so the two latencies are paid once per tile.
 template <int FMT, int DQK>
-__device__ __forceinline__ void fetch_group(RowRegs<FMT, DQK>& regs, const AttnParams& p,
-                                            const ListView& lv, int j, int qd) {
-  int idx;
-  bool is_main;
-  if (j < lv.end && list_entry(p, lv, j, idx, is_main)) regs.load(p, is_main, idx, qd);
-  else regs.zero();
+__device__ __forceinline__ void stage_load(Stage<FMT, DQK>& st, const AttnParams& p,
+                                           const ListView& lv, int j0, int ph, int pw, int lane) {
+  using S = Stage<FMT, DQK>;
+  using C = Cfg<FMT, DQK>;
+  const int row_in = lane >> 1, half = lane & 1;
+  const bool has_main = pw < S::MAIN_BLOCKS;
+  int idx[S::KS];
+#pragma unroll
+  for (int jj = 0; jj < S::KS; ++jj)
+    idx[jj] = list_index(lv, j0 + 16 * (ph * S::KS + jj) + row_in);
+#pragma unroll
+  for (int jj = 0; jj < S::KS; ++jj) {
+    const int j = ph * S::KS + jj;
+    const bool is_main = (j0 + 16 * j + row_in) < lv.len;
+    const int ntok = is_main ? p.n_tok : p.extra_n_tok;
+    const bool valid = idx[jj] >= 0 && idx[jj] < ntok;
+    const uint8_t* kv = is_main ? p.kv : p.extra_kv;
+    const int64_t stride = is_main ? p.stride_kv : p.stride_extra_kv;
+    const uint8_t* row = nullptr;
+    const uint8_t* scl = nullptr;
+    if (valid) {
+      if constexpr (C::PAGED) {
+        using T = KvTraits<FMT>;
+        const int pb = is_main ? p.page_block : p.extra_page_block;
+        const int sh = is_main ? p.page_shift : p.extra_page_shift;
+        const int page = sh >= 0 ? (idx[jj] >> sh) : (idx[jj] / pb);
+        const int r = idx[jj] - page * pb;
+        const uint8_t* pbase = kv + static_cast<int64_t>(page) * stride;
+        row = pbase + r * T::ROW_BYTES;
+        scl = pbase + pb * T::ROW_BYTES + r * T::SLOTS;
+      } else
+        row = kv + static_cast<int64_t>(idx[jj]) * stride * 2;
+    }
+#pragma unroll
+    for (int k = 0; k < S::NV; ++k) st.d[jj][k] = make_uint4(0, 0, 0, 0);
+    st.sc[jj] = 0x7f7f7f7fu;
+    if (valid && has_main) {
+      if constexpr (C::PAGED) {
+        st.d[jj][0] = ldg16(row + 64 * pw + 32 * half);
+        st.d[jj][1] = ldg16(row + 64 * pw + 32 * half + 16);
+        const int tile_no = pw * 64 / KvTraits<FMT>::TILE;
+        st.sc[jj] = __ldg(reinterpret_cast<const uint32_t*>(scl) + (tile_no >> 2));
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) st.d[jj][k] = ldg16(row + 128 * pw + 64 * half + 16 * k);
+      }
+    }
+    if (S::HAS_LAST && j == pw) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) st.last[k] = make_uint4(0, 0, 0, 0);
+      if (valid) {
+        const uint8_t* src = row + (C::PAGED ? C::NOPE_SEGS * 64 : S::MAIN_BLOCKS * 128) + 64 * half;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) st.last[k] = ldg16(src + 16 * k);
+      }
+    }
+  }
+}
+
+// Convert and store k-step j (held at register slot jj) into the swizzled K tile.
+template <int FMT, int DQK>
+__device__ __forceinline__ void stage_store(const Stage<FMT, DQK>& st, uint32_t sK, int j, int jj,
+                                            int pw, int lane) {
+  using S = Stage<FMT, DQK>;
+  using C = Cfg<FMT, DQK>;
+  const int row_in = lane >> 1, half = lane & 1;
+  const int row = 16 * j + row_in, x = row_in & 7;
+  const uint32_t rbase = sK + row * 128;
+  if (pw < S::MAIN_BLOCKS) {
+    const uint32_t a = rbase + pw * KBLOCK_BYTES;
+    if constexpr (C::PAGED) {
+      const int tile_no = pw * 64 / KvTraits<FMT>::TILE;
+      const ScaleMul mul = make_scale_mul((st.sc[jj] >> (8 * (tile_no & 3))) & 0xffu);
+      uint32_t o[16];
+      dequant4_fast(st.d[jj][0].x, mul, o[0], o[1]);
+      dequant4_fast(st.d[jj][0].y, mul, o[2], o[3]);
+      dequant4_fast(st.d[jj][0].z, mul, o[4], o[5]);
+      dequant4_fast(st.d[jj][0].w, mul, o[6], o[7]);
+      dequant4_fast(st.d[jj][1].x, mul, o[8], o[9]);
+      dequant4_fast(st.d[jj][1].y, mul, o[10], o[11]);
+      dequant4_fast(st.d[jj][1].z, mul, o[12], o[13]);
+      dequant4_fast(st.d[jj][1].w, mul, o[14], o[15]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        st_shared_v4(a + (((4 * half + k) ^ x) << 4), o[4 * k], o[4 * k + 1], o[4 * k + 2],
+                     o[4 * k + 3]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        st_shared_v4(a + (((4 * half + k) ^ x) << 4), st.d[jj][k].x, st.d[jj][k].y, st.d[jj][k].z,
+                     st.d[jj][k].w);
+    }
+  }
+  if (S::HAS_LAST && j == pw) {
+    const uint32_t a = rbase + (C::NB - 1) * KBLOCK_BYTES;
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      st_shared_v4(a + (((4 * half + k) ^ x) << 4), st.last[k].x, st.last[k].y, st.last[k].z,
+                   st.last[k].w);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -220,6 +281,7 @@ template <int FMT, int DQK>
 __global__ void __launch_bounds__(THREADS, 1)
 sm100_attn_kernel(const AttnParams p) {
   using C = Cfg<FMT, DQK>;
+  using S = Stage<FMT, DQK>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -229,6 +291,7 @@ sm100_attn_kernel(const AttnParams p) {
   Ctrl& ctrl = *reinterpret_cast<Ctrl*>(sm + C::K_BYTES + C::Q_BYTES + C::P_BYTES);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) stamp(p, 0);
   const int req = blockIdx.x, hb = blockIdx.y, split = blockIdx.z;
   const int head0 = hb * HEADS;
   const int heads_here = min(HEADS, p.h_q - head0);
@@ -236,6 +299,8 @@ sm100_attn_kernel(const AttnParams p) {
   const bool decode = p.mode == MODE_DECODE;
   const bool mask_invalid = !decode || (p.flags & DSV4_FLAG_MASK_INVALID);
   const bool split_out = p.n_splits > 1;
+  const bool is_producer = warp >= SOFTMAX_WARPS;
+  const int pw = warp - SOFTMAX_WARPS;
 
   ListView lv;
   int xlen;
@@ -276,127 +341,154 @@ sm100_attn_kernel(const AttnParams p) {
     return;
   }
 
-  // ---- set-up: barriers, TMEM, Q ---------------------------------------------------
-  if (tid == 0) {
-    mbar_init(smem_u32(&ctrl.k_full), PRODUCER_WARPS);
-    mbar_init(smem_u32(&ctrl.s_full), 1);
-    mbar_init(smem_u32(&ctrl.p_full), SOFTMAX_WARPS);
-    mbar_init(smem_u32(&ctrl.o_done), 1);
-    for (int i = 0; i < PRODUCER_WARPS; ++i) mbar_init(smem_u32(&ctrl.kv_free[i]), 1);
-    ctrl.resc[0] = ctrl.resc[1] = 0;
-    mbar_init_fence();
-  }
-  if (tid < HEADS) {
-    ctrl.mref[tid] = -INFINITY;
-    ctrl.mtrue[tid] = -INFINITY;
-    ctrl.alpha[tid] = 1.f;
-  }
-  if (warp == MMA_WARP) {
-    tmem_alloc(smem_u32(&ctrl.tmem), TMEM_COLS);
-    tmem_relinquish();
-  }
-  {
-    // Q[head][d] -> blocks [d/64][head][64], 128-byte swizzle; absent heads are zero.
-    const __nv_bfloat16* qrow0 = p.q + bi * p.stride_q_b + si * p.stride_q_s + head0 * p.stride_q_h;
-    for (int i = tid; i < HEADS * C::NB * 8; i += THREADS) {
-      const int h = i / (C::NB * 8), cc = i % (C::NB * 8), kb = cc >> 3, ch = cc & 7;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (h < heads_here)
-        v = __ldg(reinterpret_cast<const uint4*>(qrow0 + h * p.stride_q_h) + cc);
-      st_shared_v4(sQ + kb * QBLOCK_BYTES + h * 128 + ((ch ^ (h & 7)) << 4), v.x, v.y, v.z, v.w);
+  // ---- set-up (run by every warp inside its own role branch, so that each role's
+  // register budget is in force before any of its long-lived values exist) ----------
+  auto cta_setup = [&]() {
+    if (tid == 0) {
+      mbar_init(smem_u32(&ctrl.k_full), PRODUCER_WARPS);
+      mbar_init(smem_u32(&ctrl.s_full), 1);
+      mbar_init(smem_u32(&ctrl.p_full), SOFTMAX_WARPS);
+      mbar_init(smem_u32(&ctrl.o_done), 1);
+      for (int i = 0; i < 8; ++i) mbar_init(smem_u32(&ctrl.kv_free[i]), 1);
+      ctrl.resc[0] = ctrl.resc[1] = 0;
+      ctrl.fail = 0;
+      mbar_init_fence();
     }
-  }
-  fence_async_smem();
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem = ctrl.tmem;
+    if (tid < HEADS) {
+      ctrl.mref[tid] = -INFINITY;
+      ctrl.muse[tid] = 0.f;
+      ctrl.mtrue[tid] = -INFINITY;
+      ctrl.alpha[tid] = 1.f;
+    }
+    if (warp == 0) {
+      tmem_alloc(smem_u32(&ctrl.tmem), TMEM_COLS);
+      tmem_relinquish();
+    }
+    // Q[head][d] -> blocks [d/64][head][64], 128-byte swizzle; absent heads are zero.
+    // Loads are issued in batches so their latencies overlap.
+    const __nv_bfloat16* qrow0 = p.q + bi * p.stride_q_b + si * p.stride_q_s + head0 * p.stride_q_h;
+    constexpr int Q_CHUNKS = HEADS * C::NB * 8;
+    constexpr int Q_BATCH = 3;
+    constexpr int Q_ITERS = (Q_CHUNKS + THREADS * Q_BATCH - 1) / (THREADS * Q_BATCH);
+#pragma unroll 1
+    for (int ob = 0; ob < Q_ITERS; ++ob) {
+      uint4 qv[Q_BATCH];
+#pragma unroll
+      for (int it = 0; it < Q_BATCH; ++it) {
+        const int i = tid + (ob * Q_BATCH + it) * THREADS;
+        const int h = i / (C::NB * 8), cc = i % (C::NB * 8);
+        qv[it] = make_uint4(0, 0, 0, 0);
+        if (i < Q_CHUNKS && h < heads_here)
+          qv[it] = __ldg(reinterpret_cast<const uint4*>(qrow0 + h * p.stride_q_h) + cc);
+      }
+#pragma unroll
+      for (int it = 0; it < Q_BATCH; ++it) {
+        const int i = tid + (ob * Q_BATCH + it) * THREADS;
+        const int h = i / (C::NB * 8), cc = i % (C::NB * 8), kb = cc >> 3, ch = cc & 7;
+        if (i < Q_CHUNKS)
+          st_shared_v4(sQ + kb * QBLOCK_BYTES + h * 128 + ((ch ^ (h & 7)) << 4), qv[it].x, qv[it].y,
+                       qv[it].z, qv[it].w);
+      }
+    }
+    fence_async_smem();
+    tc_fence_before_sync();
+    bar_sync(3, THREADS);
+    tc_fence_after_sync();
+    if (tid == 0) stamp(p, 1);
+  };
+#define TSTAMP(t, k) do { if ((t) < PROF_MAX_TILES) stamp(p, PROF_TILE0 + (t) * PROF_PER_TILE + (k)); } while (0)
 
   const uint32_t bar_k_full = smem_u32(&ctrl.k_full), bar_s_full = smem_u32(&ctrl.s_full);
   const uint32_t bar_p_full = smem_u32(&ctrl.p_full), bar_o_done = smem_u32(&ctrl.o_done);
+  const uint32_t bar_kv_free0 = smem_u32(&ctrl.kv_free[0]);
 
-  if (warp == MMA_WARP) {
-    // =========================== MMA issue ==========================================
-    if (lane == 0) {
-      const uint32_t idesc_qk = make_idesc_bf16(TILE, HEADS, 0, 0);
-      const uint32_t idesc_pv = make_idesc_bf16(128, HEADS, 1, 1);
-      const uint64_t dK = make_smem_desc(sK, 16, 1024, SWZ_128B);            // K-major view
-      const uint64_t dQ = make_smem_desc(sQ, 16, 1024, SWZ_128B);
-      const uint64_t dV = make_smem_desc(sK, KBLOCK_BYTES, 1024, SWZ_128B);  // MN-major view
-      const uint64_t dP = make_smem_desc(sP, 1024, 1024, SWZ_128B);
-      bool ok = true;
-      for (int t = 0; t < n_tiles && ok; ++t) {
-        if (!mbar_wait(bar_k_full, t & 1)) { atomicExch(&g_attn_error, ERR_KFULL); ok = false; break; }
-        tc_fence_after_sync();
-#pragma unroll 1
-        for (int kb = 0; kb < C::NB; ++kb) {
+  // ---- MMA issue: done by thread 0 (lane 0 of softmax warp 0), in between its softmax
+  // steps; the tensor core runs asynchronously and reports through mbarriers ---------
+  const uint32_t idesc_qk = make_idesc_bf16(TILE, HEADS, 0, 0);
+  const uint32_t idesc_pv = make_idesc_bf16(128, HEADS, 1, 1);
+  const uint64_t dK = make_smem_desc(sK, 16, 1024, SWZ_128B);            // K-major view
+  const uint64_t dQ = make_smem_desc(sQ, 16, 1024, SWZ_128B);
+  const uint64_t dV = make_smem_desc(sK, KBLOCK_BYTES, 1024, SWZ_128B);  // MN-major view
+  const uint64_t dP = make_smem_desc(sP, 1024, 1024, SWZ_128B);
+  const uint32_t dK_lo = static_cast<uint32_t>(dK), dK_hi = static_cast<uint32_t>(dK >> 32);
+  const uint32_t dQ_lo = static_cast<uint32_t>(dQ), dQ_hi = static_cast<uint32_t>(dQ >> 32);
+  const uint32_t dV_lo = static_cast<uint32_t>(dV), dV_hi = static_cast<uint32_t>(dV >> 32);
+  const uint32_t dP_lo = static_cast<uint32_t>(dP), dP_hi = static_cast<uint32_t>(dP >> 32);
+  auto issue_qk = [&](uint32_t tmem, int t) -> bool {
+    if (!mbar_wait(bar_k_full, t & 1)) { atomicExch(&g_attn_error, ERR_KFULL); return false; }
+    tc_fence_after_sync();
+    TSTAMP(t, 1);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_bf16(tmem + COL_S, desc_advance(dK, kb * KBLOCK_BYTES + ks * 32),
-                      desc_advance(dQ, kb * QBLOCK_BYTES + ks * 32), idesc_qk, (kb | ks) != 0);
-        }
-        umma_commit(bar_s_full);
-        if (!mbar_wait(bar_p_full, t & 1)) { atomicExch(&g_attn_error, ERR_PFULL); ok = false; break; }
-        tc_fence_after_sync();
-#pragma unroll 1
-        for (int j = 0; j < TILE / 16; ++j) {
+    for (int kb = 0; kb < C::NB; ++kb) {
 #pragma unroll
-          for (int m = 0; m < D_V / 128; ++m)
-            umma_bf16(tmem + COL_O + m * HEADS,
-                      desc_advance(dV, m * 2 * KBLOCK_BYTES + j * 2048),
-                      desc_advance(dP, j * 2048), idesc_pv, (t | j) != 0);
-          umma_commit(smem_u32(&ctrl.kv_free[j]));
-        }
-      }
-      umma_commit(bar_o_done);
+      for (int ks = 0; ks < 4; ++ks)
+        umma_bf16_lohi(tmem + COL_S, dK_lo + ((kb * KBLOCK_BYTES + ks * 32) >> 4), dK_hi,
+                       dQ_lo + ((kb * QBLOCK_BYTES + ks * 32) >> 4), dQ_hi, idesc_qk,
+                       (kb | ks) != 0);
     }
-    __syncwarp();
-  } else if (warp >= SOFTMAX_WARPS) {
+    umma_commit(bar_s_full);
+    return true;
+  };
+  auto issue_pv = [&](uint32_t tmem, int t, bool last) -> bool {
+    if (!mbar_wait(bar_p_full, t & 1)) { atomicExch(&g_attn_error, ERR_PFULL); return false; }
+    tc_fence_after_sync();
+    TSTAMP(t, 5);
+#pragma unroll
+    for (int j = 0; j < TILE / 16; ++j) {
+#pragma unroll
+      for (int m = 0; m < D_V / 128; ++m)
+        umma_bf16_lohi(tmem + COL_O + m * HEADS, dV_lo + ((m * 2 * KBLOCK_BYTES + j * 2048) >> 4),
+                       dV_hi, dP_lo + ((j * 2048) >> 4), dP_hi, idesc_pv, (t | j) != 0);
+      umma_commit(bar_kv_free0 + 8 * j);
+    }
+    if (last) umma_commit(bar_o_done);
+    return true;
+  };
+
+  uint32_t tmem;
+  if (is_producer) {
     // =========================== producers ==========================================
-    const int pw = warp - SOFTMAX_WARPS, r = lane >> 2, qd = lane & 3;
-    const int row0 = 16 * pw + r, row1 = row0 + 8;
-    const uint32_t bar_free = smem_u32(&ctrl.kv_free[pw]);
-    RowRegs<FMT, DQK> g0;
-    fetch_group(g0, p, lv, lv.begin + row0, qd);
-    if constexpr (C::PAGED) {
-      RowRegs<FMT, DQK> g1;
-      fetch_group(g1, p, lv, lv.begin + row1, qd);
-      for (int t = 0; t < n_tiles; ++t) {
-        if (t > 0 && !mbar_wait(bar_free, (t - 1) & 1)) { atomicExch(&g_attn_error, ERR_KVFREE); break; }
-        g0.store(sK, row0, r, qd);
-        g1.store(sK, row1, r, qd);
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_k_full);
-        if (t + 1 < n_tiles) {
-          const int j = lv.begin + (t + 1) * TILE;
-          fetch_group(g0, p, lv, j + row0, qd);
-          fetch_group(g1, p, lv, j + row1, qd);
+    S stage;
+    stage_load(stage, p, lv, lv.begin, 0, pw, lane);   // first gather in flight before set-up
+    cta_setup();
+    tmem = ctrl.tmem;
+    bool ok = true;
+    for (int t = 0; t < n_tiles && ok; ++t) {
+      const int j0 = lv.begin + t * TILE;
+#pragma unroll
+      for (int ph = 0; ph < S::PHASES; ++ph) {
+        if (ph > 0) stage_load(stage, p, lv, j0, ph, pw, lane);
+#pragma unroll
+        for (int jj = 0; jj < S::KS; ++jj) {
+          const int j = ph * S::KS + jj;
+          if (t > 0 && ok && !mbar_wait_warp(bar_kv_free0 + 8 * j, (t - 1) & 1, lane)) {
+            atomicExch(&g_attn_error, ERR_KVFREE);
+            ok = false;
+          }
+          if (pw == 0 && lane == 0 && jj == 0 && ph == 0) TSTAMP(t, 6);
+          if (ok) stage_store(stage, sK, j, jj, pw, lane);
         }
       }
-    } else {
-      // BF16 rows are twice as wide: one group of 8 rows is staged ahead, the
-      // second is fetched once the tile rows are free.
-      for (int t = 0; t < n_tiles; ++t) {
-        if (t > 0 && !mbar_wait(bar_free, (t - 1) & 1)) { atomicExch(&g_attn_error, ERR_KVFREE); break; }
-        const int j = lv.begin + t * TILE;
-        g0.store(sK, row0, r, qd);
-        fetch_group(g0, p, lv, j + row1, qd);
-        g0.store(sK, row1, r, qd);
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_k_full);
-        if (t + 1 < n_tiles) fetch_group(g0, p, lv, j + TILE + row0, qd);
-      }
+      if (!ok) break;
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_k_full);
+      if (pw == 0 && lane == 0) TSTAMP(t, 0);
+      if (pw == PRODUCER_WARPS - 1 && lane == 0) TSTAMP(t, 7);
+      if (t + 1 < n_tiles) stage_load(stage, p, lv, j0 + TILE, 0, pw, lane);
     }
   } else {
-    // =========================== softmax + epilogue =================================
-    const int row = tid;                                   // tile row == TMEM lane
-    const uint32_t tlane = static_cast<uint32_t>(warp * 32) << 16;
+    // =========================== softmax ============================================
+    // Warp (lg, ch): TMEM lanes 32*lg.. (tile rows), head columns 32*ch..32*ch+31.
+    cta_setup();
+    tmem = ctrl.tmem;
+    const int lg = warp & 3, ch = warp >> 2;
+    const int row = lg * 32 + lane;
+    const uint32_t tlane = static_cast<uint32_t>(lg * 32) << 16;
     const float cs = p.sm_scale * LOG2E;
-    float lsum[HEADS];
+    float lsum[32];
 #pragma unroll
-    for (int i = 0; i < HEADS; ++i) lsum[i] = 0.f;
+    for (int i = 0; i < 32; ++i) lsum[i] = 0.f;
     bool ok = true;
 
     for (int t = 0; t < n_tiles; ++t) {
@@ -411,48 +503,53 @@ sm100_attn_kernel(const AttnParams p) {
           masked = !valid && mask_invalid;
         }
       }
-      if (!mbar_wait(bar_s_full, t & 1)) { atomicExch(&g_attn_error, ERR_SFULL); ok = false; break; }
+      if (tid == 0) issue_qk(tmem, t);
+      __syncwarp();
+      if (!mbar_wait_warp(bar_s_full, t & 1, lane)) { atomicExch(&g_attn_error, ERR_SFULL); ok = false; break; }
       tc_fence_after_sync();
+      if (tid == 0) TSTAMP(t, 2);
 
       // pass 1: per-head max over the tile's rows
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      {
         float v[32];
         uint32_t ra[16], rb[16];
-        tmem_ld16(tmem + tlane + COL_S + half * 32, ra);
-        tmem_ld16(tmem + tlane + COL_S + half * 32 + 16, rb);
+        tmem_ld16(tmem + tlane + COL_S + ch * 32, ra);
+        tmem_ld16(tmem + tlane + COL_S + ch * 32 + 16, rb);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           v[i] = masked ? -INFINITY : __uint_as_float(ra[i]);
           v[16 + i] = masked ? -INFINITY : __uint_as_float(rb[i]);
         }
-        ctrl.wred[warp][half * 32 + lane] = warp_col_reduce32<true>(v, lane);
+        ctrl.wred[lg][ch * 32 + lane] = warp_col_reduce32<true>(v, lane);
       }
       bar_sync(1, SOFTMAX_WARPS * 32);
-      if (row < HEADS) {
-        float tm = fmaxf(fmaxf(ctrl.wred[0][row], ctrl.wred[1][row]),
-                         fmaxf(ctrl.wred[2][row], ctrl.wred[3][row])) * cs;
-        ctrl.mtrue[row] = fmaxf(ctrl.mtrue[row], tm);
-        const float mr = ctrl.mref[row];
+      if (tid < HEADS) {
+        float tm = fmaxf(fmaxf(ctrl.wred[0][tid], ctrl.wred[1][tid]),
+                         fmaxf(ctrl.wred[2][tid], ctrl.wred[3][tid])) * cs;
+        ctrl.mtrue[tid] = fmaxf(ctrl.mtrue[tid], tm);
+        const float mr = ctrl.mref[tid];
         float alpha = 1.f;
         if (tm > mr + RESCALE_THRESHOLD) {                 // also the first finite max
           alpha = (mr == -INFINITY) ? 0.f : ex2(mr - tm);
-          ctrl.mref[row] = tm;
+          ctrl.mref[tid] = tm;
+          ctrl.muse[tid] = tm;
           ctrl.resc[t & 1] = 1;
         }
-        ctrl.alpha[row] = alpha;
+        ctrl.alpha[tid] = alpha;
       }
-      if (row == 64) ctrl.resc[(t + 1) & 1] = 0;
+      if (tid == 64) ctrl.resc[(t + 1) & 1] = 0;
       bar_sync(1, SOFTMAX_WARPS * 32);
+      if (tid == 0) TSTAMP(t, 3);
 
       if (ctrl.resc[t & 1]) {
 #pragma unroll
-        for (int i = 0; i < HEADS; ++i) lsum[i] *= ctrl.alpha[i];
+        for (int i = 0; i < 32; ++i) lsum[i] *= ctrl.alpha[ch * 32 + i];
         if (t > 0) {
+          // this warp rescales O^T slices 2*ch and 2*ch+1 for its 32 TMEM lanes
 #pragma unroll 1
-          for (int c = 0; c < (D_V / 128) * (HEADS / 16); ++c) {
-            const int m = c / (HEADS / 16), c4 = c % (HEADS / 16);
+          for (int c = 0; c < 2 * (HEADS / 16); ++c) {
+            const int m = 2 * ch + c / (HEADS / 16), c4 = c % (HEADS / 16);
             uint32_t o[16];
             const uint32_t addr = tmem + tlane + COL_O + m * HEADS + c4 * 16;
             tmem_ld16(addr, o);
@@ -466,79 +563,106 @@ sm100_attn_kernel(const AttnParams p) {
         }
       }
 
-      // pass 2: p = 2^(s*c - mref), denominators, P^T row to shared memory
-#pragma unroll
-      for (int c4 = 0; c4 < HEADS / 16; ++c4) {
-        uint32_t s[16];
-        tmem_ld16(tmem + tlane + COL_S + c4 * 16, s);
+      // pass 2: p = 2^(s*c - mref), denominators, this warp's half of the P^T row
+      {
+        const uint32_t prow = sP + row * 128;
+        const int x = row & 7;
+        // TMEM loads are warp-collective: every lane takes part even if its row is masked.
+        uint32_t sa[16], sb[16];
+        tmem_ld16(tmem + tlane + COL_S + ch * 32, sa);
+        tmem_ld16(tmem + tlane + COL_S + ch * 32 + 16, sb);
         tmem_ld_wait();
-        uint32_t packed[8];
+        if (__any_sync(0xffffffffu, masked)) {          // rare: ragged tile or masked entries
+          const uint32_t ninf = __float_as_uint(-INFINITY);
 #pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-          float m0 = ctrl.mref[c4 * 16 + i], m1 = ctrl.mref[c4 * 16 + i + 1];
-          m0 = (m0 == -INFINITY) ? 0.f : m0;
-          m1 = (m1 == -INFINITY) ? 0.f : m1;
-          float p0 = masked ? 0.f : ex2(fmaf(__uint_as_float(s[i]), cs, -m0));
-          float p1 = masked ? 0.f : ex2(fmaf(__uint_as_float(s[i + 1]), cs, -m1));
-          __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-          // denominators use the rounded probabilities that P.V will see
-          lsum[c4 * 16 + i] += __low2float(pk);
-          lsum[c4 * 16 + i + 1] += __high2float(pk);
-          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+          for (int i = 0; i < 16; ++i) {
+            sa[i] = masked ? ninf : sa[i];
+            sb[i] = masked ? ninf : sb[i];
+          }
         }
-        const uint32_t a = sP + row * 128;
-        st_shared_v4(a + (((2 * c4) ^ (row & 7)) << 4), packed[0], packed[1], packed[2], packed[3]);
-        st_shared_v4(a + (((2 * c4 + 1) ^ (row & 7)) << 4), packed[4], packed[5], packed[6], packed[7]);
+        uint32_t pk[16];
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) {
+          const float4 mu = *reinterpret_cast<const float4*>(&ctrl.muse[ch * 32 + q4 * 4]);
+          const uint32_t* src = q4 < 4 ? &sa[q4 * 4] : &sb[(q4 - 4) * 4];
+          const float p0 = ex2(fmaf(__uint_as_float(src[0]), cs, -mu.x));
+          const float p1 = ex2(fmaf(__uint_as_float(src[1]), cs, -mu.y));
+          const float p2 = ex2(fmaf(__uint_as_float(src[2]), cs, -mu.z));
+          const float p3 = ex2(fmaf(__uint_as_float(src[3]), cs, -mu.w));
+          lsum[q4 * 4 + 0] += p0;
+          lsum[q4 * 4 + 1] += p1;
+          lsum[q4 * 4 + 2] += p2;
+          lsum[q4 * 4 + 3] += p3;
+          __nv_bfloat162 a = __floats2bfloat162_rn(p0, p1), b = __floats2bfloat162_rn(p2, p3);
+          pk[q4 * 2] = *reinterpret_cast<uint32_t*>(&a);
+          pk[q4 * 2 + 1] = *reinterpret_cast<uint32_t*>(&b);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          st_shared_v4(prow + (((4 * ch + k) ^ x) << 4), pk[4 * k], pk[4 * k + 1], pk[4 * k + 2],
+                       pk[4 * k + 3]);
       }
       fence_async_smem();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_p_full);
+      if (tid == 0) {
+        TSTAMP(t, 4);
+        issue_pv(tmem, t, t + 1 == n_tiles);
+      }
+      __syncwarp();
     }
 
-    // ---- epilogue ------------------------------------------------------------------
-    if (ok && !mbar_wait(bar_o_done, 0)) { atomicExch(&g_attn_error, ERR_ODONE); ok = false; }
+    // ---- final denominators and output factors -------------------------------------
+    if (ok && !mbar_wait_warp(bar_o_done, 0, lane)) { atomicExch(&g_attn_error, ERR_ODONE); ok = false; }
     tc_fence_after_sync();
-    if (ok) {
+    if (tid == 0) stamp(p, 3);
+    if (!ok) ctrl.fail = 1;
+    {
+      float v[32];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = lsum[half * 32 + i];
-        ctrl.wred[warp][half * 32 + lane] = warp_col_reduce32<false>(v, lane);
-      }
-      bar_sync(1, SOFTMAX_WARPS * 32);
-      if (row < HEADS) {
-        const float l = ctrl.wred[0][row] + ctrl.wred[1][row] + ctrl.wred[2][row] + ctrl.wred[3][row];
-        const float mr = ctrl.mref[row];
-        float f;
-        if (split_out) {
-          const bool empty = !(l > 0.f);
-          f = empty ? 0.f : 1.f / l;
-          if (row < heads_here) p.lse_accum[acc_slot0 + row] = empty ? -INFINITY : logf(l) + mr * LN2;
-        } else {
-          const bool has_sink = p.sink != nullptr;
-          float lse_v, ml_v;
-          f = finalize_row(p.mode, mr == -INFINITY ? -INFINITY : mr * LN2, l, has_sink,
-                           (has_sink && row < heads_here) ? p.sink[head0 + row] : 0.f, lse_v, ml_v);
-          if (row < heads_here) {
-            p.lse[bi * p.stride_lse_b + si * p.stride_lse_s + (head0 + row) * p.stride_lse_h] = lse_v;
-            if (p.max_logits)
-              p.max_logits[bi * p.stride_ml_b + head0 + row] =
-                  (ml_v == -INFINITY) ? -INFINITY : ctrl.mtrue[row] * LN2;
-          }
+      for (int i = 0; i < 32; ++i) v[i] = lsum[i];
+      ctrl.wred[lg][ch * 32 + lane] = warp_col_reduce32<false>(v, lane);
+    }
+    bar_sync(1, SOFTMAX_WARPS * 32);
+    if (tid < HEADS && !ctrl.fail) {
+      const float l = ctrl.wred[0][tid] + ctrl.wred[1][tid] + ctrl.wred[2][tid] + ctrl.wred[3][tid];
+      const float mr = ctrl.mref[tid];
+      float f;
+      if (split_out) {
+        const bool empty = !(l > 0.f);
+        f = empty ? 0.f : 1.f / l;
+        if (tid < heads_here) p.lse_accum[acc_slot0 + tid] = empty ? -INFINITY : logf(l) + mr * LN2;
+      } else {
+        const bool has_sink = p.sink != nullptr;
+        float lse_v, ml_v;
+        f = finalize_row(p.mode, mr == -INFINITY ? -INFINITY : mr * LN2, l, has_sink,
+                         (has_sink && tid < heads_here) ? p.sink[head0 + tid] : 0.f, lse_v, ml_v);
+        if (tid < heads_here) {
+          p.lse[bi * p.stride_lse_b + si * p.stride_lse_s + (head0 + tid) * p.stride_lse_h] = lse_v;
+          if (p.max_logits)
+            p.max_logits[bi * p.stride_ml_b + head0 + tid] =
+                (ml_v == -INFINITY) ? -INFINITY : ctrl.mtrue[tid] * LN2;
         }
-        ctrl.alpha[row] = f;
       }
-      bar_sync(1, SOFTMAX_WARPS * 32);
-      // O^T[d, head] -> out[head, d]: for a fixed head a warp writes 32 consecutive d.
-#pragma unroll 1
-      for (int c = 0; c < (D_V / 128) * (HEADS / 16); ++c) {
-        const int m = c / (HEADS / 16), c4 = c % (HEADS / 16);
+      ctrl.alpha[tid] = f;
+    }
+  }
+
+  // ---- epilogue: all 16 softmax + producer warps drain O^T -------------------------
+  {
+    bar_sync(2, THREADS);
+    tc_fence_after_sync();
+    if (!ctrl.fail) {
+      // warp w: O^T slice m = w / 4, TMEM lanes 32 * (w % 4)..; d = 128 m + lane offset.
+      const int m = warp >> 2, lg = warp & 3;
+      const uint32_t tl = static_cast<uint32_t>(lg * 32) << 16;
+      const int d = m * 128 + lg * 32 + lane;
+#pragma unroll
+      for (int c4 = 0; c4 < HEADS / 16; ++c4) {
         uint32_t o[16];
-        tmem_ld16(tmem + tlane + COL_O + m * HEADS + c4 * 16, o);
+        tmem_ld16(tmem + tl + COL_O + m * HEADS + c4 * 16, o);
         tmem_ld_wait();
-        const int d = m * 128 + row;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const int h = c4 * 16 + i;
@@ -553,9 +677,11 @@ sm100_attn_kernel(const AttnParams p) {
   }
 
   // ---- teardown --------------------------------------------------------------------
+  if (tid == 0) stamp(p, 4);
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == MMA_WARP) tmem_dealloc(tmem, TMEM_COLS);
+  if (tid == 0) stamp(p, 5);
+  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 template <int FMT, int DQK>

@@ -67,6 +67,7 @@ SYMBOLS = {
     "dsv4_kv_store": (C.c_int, [C.POINTER(StoreArgs), vp]),
     "dsv4_gather_dequant": (C.c_int, [vp, i64, i32, i32, i32, vp, i32, vp, i32, vp]),
     "dsv4_device_status": (C.c_int, [C.POINTER(C.c_int32), C.c_int]),
+    "dsv4_debug_set_timeline": (C.c_int, [vp]),
     "dsv4_umma_selftest": (C.c_int, [C.c_int, C.c_int, C.c_int, vp, vp, vp, vp, vp]),
 }
 

@@ -214,6 +214,11 @@ int dsv4_device_info(int device, int* major, int* minor, int* num_sms);
  * loop need not call it; the tests do after every launch.                             */
 int dsv4_device_status(int32_t* status_out, int reset);
 
+/* Debug aid: give the attention kernels a device buffer of >= 128 int64 into
+ * which CTA (0,0,0) of every later launch writes SM cycle-counter stamps of its
+ * pipeline stages (null switches it off).  Process-wide; not for production.           */
+int dsv4_debug_set_timeline(void* device_buffer);
+
 /* Text for a status code; the last CUDA error string seen by this thread.             */
 const char* dsv4_strerror(int status);
 const char* dsv4_last_cuda_error(void);
