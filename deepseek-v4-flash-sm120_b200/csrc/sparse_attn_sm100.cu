@@ -13,24 +13,26 @@
 // (contraction over d) for the first product and as MN-major (contraction over
 // tokens) for the second.  With d_qk = 576 the tile (144 KB) and Q (72 KB) leave
 // no room for a second tile or a staging ring, so gathered rows are staged in
-// REGISTERS: each producer warp owns one 64-column block of every tile row,
-// issues the 16-byte loads of the next tile while the current one is being
-// multiplied, and writes each group of 16 rows (dequantised to BF16) as soon as
-// the P.V step that last read those rows has retired.  P^T (16 KB) reuses the RoPE block of the tile, which only
-// Q.K^T reads, when d_qk = 576.
+// REGISTERS: every warp owns one 64-column block of 8 rows of each 16-row
+// "k-step" of the tile, issues the 16-byte loads of the next tile while the
+// current one is being multiplied, and writes each k-step (dequantised to BF16)
+// as soon as the P.V MMA step that last read those 16 rows has retired.  P^T
+// (16 KB) reuses the RoPE block of the tile, which only Q.K^T reads, when
+// d_qk = 576.
 //
-// Warp roles (16 warps x 128 registers fill the register file): 0-7 softmax (a
-// thread owns one tile row = TMEM lane and 32 of the 64 heads), 8-15 producers
-// (gather + dequantise + swizzled store).  Thread 0 also issues the MMAs, which
-// run asynchronously, in between its softmax steps; warp 0 owns TMEM.
+// All 16 warps are alike (512 threads x 128 registers = the whole register
+// file) and move through the phases of a tile together: issue next tile's loads
+// -> softmax of S^T (thread = one tile row = one TMEM lane, 16 of the 64 heads)
+// -> refill the K tile behind the P.V product.  Thread 0 also issues the MMAs,
+// which run asynchronously and report through mbarriers; warp 0 owns TMEM.
 // TMEM columns: [0,64) S^T, [64,320) the four 128-row slices of O^T.
 //
 // Softmax: running per-head reference max with lazy rescaling (O^T is touched
 // only when a head's max grows by more than 2^8), denominators accumulated per
 // thread and reduced across the 128 rows once, at the end.
 //
-// Every wait is bounded; a wait that gives up records a code in g_attn_error,
-// and the CTA drains and returns without touching its outputs further.
+// Every mbarrier wait is bounded; a wait that gives up records a code in
+// g_attn_error, and the CTA drains and returns without writing its outputs.
 #include "attn_params.cuh"
 #include "launchers.h"
 #include "sm100_ptx.cuh"
@@ -45,9 +47,10 @@ using namespace ptx;
 
 constexpr int TILE = 128;              // index entries per tile (= MMA M)
 constexpr int HEADS = 64;              // heads per CTA (= MMA N)
-constexpr int SOFTMAX_WARPS = 8, PRODUCER_WARPS = 8;
-constexpr int WORK_WARPS = SOFTMAX_WARPS + PRODUCER_WARPS;
-constexpr int THREADS = WORK_WARPS * 32;              // 512 threads x 128 registers = the whole file
+constexpr int WARPS = 16;
+constexpr int THREADS = WARPS * 32;    // 512 threads x 128 registers
+constexpr int KSTEPS = TILE / 16;      // P.V contraction steps per tile
+constexpr int COLS_PER_WARP = HEADS / (WARPS / 4);    // 16 head columns per softmax thread
 constexpr int KBLOCK_BYTES = TILE * 128;              // [128 tok][64 bf16]
 constexpr int QBLOCK_BYTES = HEADS * 128;
 constexpr uint32_t TMEM_COLS = 512;
@@ -61,15 +64,20 @@ template <int FMT, int DQK> struct Cfg {
   static constexpr bool PAGED = FMT != DSV4_KV_BF16;
   static constexpr int NB = DQK / 64;                  // 64-wide blocks of the K tile
   static constexpr int NOPE_SEGS = PAGED ? (DQK - 64) / 64 : 0;   // 64-byte FP8 segments
-  static constexpr bool P_ALIAS = (DQK == 576);        // P^T lives in the RoPE block
+  static constexpr bool P_ALIAS = (DQK == 576);        // P^T lives in the last block
   static constexpr int K_BYTES = NB * KBLOCK_BYTES;
   static constexpr int Q_BYTES = NB * QBLOCK_BYTES;
   static constexpr int P_BYTES = P_ALIAS ? 0 : TILE * 128;
+  // Blocks handled warp-per-block (8 warps x 2 row halves); a 9th block, if any
+  // (RoPE of the paged layouts, columns 512..575 of flat BF16), is handled per k-step.
+  static constexpr int MAIN_BLOCKS = PAGED ? NOPE_SEGS : (DQK == 576 ? 8 : NB);
+  static constexpr bool HAS_LAST = PAGED || DQK == 576;
+  static constexpr int LAST_SRC_OFFSET = PAGED ? NOPE_SEGS * 64 : MAIN_BLOCKS * 128;
 };
 
 struct Ctrl {
   uint64_t k_full, s_full, p_full, o_done;
-  uint64_t kv_free[8];                 // one per P.V k-step (16 tile rows)
+  uint64_t kv_free[KSTEPS];            // one per P.V k-step (16 tile rows)
   uint32_t tmem;
   int resc[2];
   int fail;
@@ -102,12 +110,17 @@ __device__ __forceinline__ uint4 ldg16(const uint8_t* p) {
   return __ldg(reinterpret_cast<const uint4*>(p));
 }
 
-// Column-wise reduction over the 32 lanes of a warp of a 32-column slice held
-// one row per lane: afterwards v[0] of lane l is the reduction of column l.
+// Column-wise reduction, over the 32 lanes of a warp, of a 16-column slice held
+// one row per lane: afterwards v[0] of lane l is the reduction of column l & 15.
 template <bool IS_MAX>
-__device__ __forceinline__ float warp_col_reduce32(float (&v)[32], int lane) {
+__device__ __forceinline__ float warp_col_reduce16(float (&v)[16], int lane) {
 #pragma unroll
-  for (int w = 16; w >= 1; w >>= 1) {
+  for (int i = 0; i < 16; ++i) {
+    const float got = __shfl_xor_sync(0xffffffffu, v[i], 16);
+    v[i] = IS_MAX ? fmaxf(v[i], got) : v[i] + got;
+  }
+#pragma unroll
+  for (int w = 8; w >= 1; w >>= 1) {
     const bool up = (lane & w) != 0;
 #pragma unroll
     for (int i = 0; i < w; ++i) {
@@ -132,36 +145,7 @@ struct ListView {
   int len, begin, end;
 };
 
-// Fetch list entry j (j < end): which cache it names and whether it is a row.
-__device__ __forceinline__ bool list_entry(const AttnParams& p, const ListView& lv, int j,
-                                           int& idx, bool& is_main) {
-  is_main = j < lv.len;
-  idx = is_main ? __ldg(lv.main_idx + j) : __ldg(lv.extra_idx + (j - lv.len));
-  const int ntok = is_main ? p.n_tok : p.extra_n_tok;
-  return idx >= 0 && idx < ntok;
-}
-
-// ---------------------------------------------------------------------------
-// Producer staging.  A tile is 8 "k-steps" of 16 rows (the rows one P.V MMA
-// step contracts over).  Producer warp pw owns column block pw (64 values) of
-// EVERY row: per k-step lane l holds half a block row (row 16j + l/2, half l&1).
-// So when P.V retires k-step j, all eight warps refill those 16 rows at once,
-// and the refill of the whole tile trails the P.V product by one k-step.
-// The last block (RoPE / columns 512..575) of k-step j is handled by warp j.
-// ---------------------------------------------------------------------------
-template <int FMT, int DQK> struct Stage {
-  using C = Cfg<FMT, DQK>;
-  static constexpr int NV = C::PAGED ? 2 : 4;             // uint4 per lane per k-step
-  static constexpr int PHASES = C::PAGED ? 1 : 2;         // BF16 rows are staged half a tile at a time
-  static constexpr int KS = 8 / PHASES;                   // k-steps held in registers at once
-  static constexpr int MAIN_BLOCKS = C::PAGED ? C::NOPE_SEGS : (DQK == 576 ? 8 : C::NB);
-  static constexpr bool HAS_LAST = C::PAGED || DQK == 576;  // a block beyond MAIN_BLOCKS exists
-  uint4 d[KS][NV];
-  uint32_t sc[KS];
-  uint4 last[4];
-};
-
-// List entry j as (index, which cache) without branching: entries past the end read as -1.
+// List entry j without branching: entries past the end of the range read as -1.
 __device__ __forceinline__ int list_index(const ListView& lv, int j) {
   const bool in_range = j < lv.end;
   const bool is_main = j < lv.len;
@@ -169,23 +153,52 @@ __device__ __forceinline__ int list_index(const ListView& lv, int j) {
   return in_range ? __ldg(src) : -1;
 }
 
-// Issue the loads of phase `ph` of the tile whose first list entry is j0.  All index
-// loads go out first, then all row loads, so the two latencies are paid once per tile.
+// ---------------------------------------------------------------------------
+// Register staging of one tile.  A tile is 8 "k-steps" of 16 rows (the rows one
+// P.V MMA step contracts over).  Warp w owns column block w & 7 (64 values) of
+// rows 8 * (w >> 3) .. +8 of EVERY k-step: lane l holds a quarter of a block row
+// (row l >> 2, quarter l & 3: 16 FP8 bytes or 16 BF16 values).  When P.V retires
+// k-step j all sixteen warps refill those 16 rows at once, so the refill of the
+// tile trails the product by one k-step.  The 9th block of k-step j, if the
+// layout has one, is handled by the two warps whose block number is j.
+// Flat BF16 rows are twice as wide, so they are staged half a tile at a time.
+// ---------------------------------------------------------------------------
+template <int FMT, int DQK> struct Stage {
+  using C = Cfg<FMT, DQK>;
+  static constexpr int NV = C::PAGED ? 1 : 2;             // uint4 per lane per k-step
+  static constexpr int PHASES = C::PAGED ? 1 : 2;
+  static constexpr int KS = KSTEPS / PHASES;              // k-steps held in registers at once
+  uint4 d[KS][NV];
+  uint32_t sc[KS];
+  uint4 last[2];
+};
+
+// The list entries this lane's staged rows come from, for the tile starting at j0.
+// Fetched one tile ahead so that the row loads never wait on an index load.
+__device__ __forceinline__ void index_load(int (&idx)[KSTEPS], const ListView& lv, int j0,
+                                           int warp, int lane) {
+  const int rh = warp >> 3, r = lane >> 2;
+#pragma unroll
+  for (int j = 0; j < KSTEPS; ++j) idx[j] = list_index(lv, j0 + 16 * j + 8 * rh + r);
+}
+
+// Issue the row loads of phase `ph` of the tile whose first list entry is j0 and whose
+// list entries are already in `tidx`.
 template <int FMT, int DQK>
 __device__ __forceinline__ void stage_load(Stage<FMT, DQK>& st, const AttnParams& p,
-                                           const ListView& lv, int j0, int ph, int pw, int lane) {
+                                           const ListView& lv, const int (&tidx)[KSTEPS], int j0,
+                                           int ph, int warp, int lane) {
   using S = Stage<FMT, DQK>;
   using C = Cfg<FMT, DQK>;
-  const int row_in = lane >> 1, half = lane & 1;
-  const bool has_main = pw < S::MAIN_BLOCKS;
+  const int blk = warp & 7, rh = warp >> 3, r = lane >> 2, q = lane & 3;
+  const bool has_main = blk < C::MAIN_BLOCKS;
   int idx[S::KS];
 #pragma unroll
-  for (int jj = 0; jj < S::KS; ++jj)
-    idx[jj] = list_index(lv, j0 + 16 * (ph * S::KS + jj) + row_in);
+  for (int jj = 0; jj < S::KS; ++jj) idx[jj] = tidx[ph * S::KS + jj];
 #pragma unroll
   for (int jj = 0; jj < S::KS; ++jj) {
     const int j = ph * S::KS + jj;
-    const bool is_main = (j0 + 16 * j + row_in) < lv.len;
+    const bool is_main = (j0 + 16 * j + 8 * rh + r) < lv.len;
     const int ntok = is_main ? p.n_tok : p.extra_n_tok;
     const bool valid = idx[jj] >= 0 && idx[jj] < ntok;
     const uint8_t* kv = is_main ? p.kv : p.extra_kv;
@@ -198,34 +211,32 @@ __device__ __forceinline__ void stage_load(Stage<FMT, DQK>& st, const AttnParams
         const int pb = is_main ? p.page_block : p.extra_page_block;
         const int sh = is_main ? p.page_shift : p.extra_page_shift;
         const int page = sh >= 0 ? (idx[jj] >> sh) : (idx[jj] / pb);
-        const int r = idx[jj] - page * pb;
+        const int rr = idx[jj] - page * pb;
         const uint8_t* pbase = kv + static_cast<int64_t>(page) * stride;
-        row = pbase + r * T::ROW_BYTES;
-        scl = pbase + pb * T::ROW_BYTES + r * T::SLOTS;
-      } else
+        row = pbase + rr * T::ROW_BYTES;
+        scl = pbase + pb * T::ROW_BYTES + rr * T::SLOTS;
+      } else {
         row = kv + static_cast<int64_t>(idx[jj]) * stride * 2;
+      }
     }
 #pragma unroll
     for (int k = 0; k < S::NV; ++k) st.d[jj][k] = make_uint4(0, 0, 0, 0);
     st.sc[jj] = 0x7f7f7f7fu;
     if (valid && has_main) {
       if constexpr (C::PAGED) {
-        st.d[jj][0] = ldg16(row + 64 * pw + 32 * half);
-        st.d[jj][1] = ldg16(row + 64 * pw + 32 * half + 16);
-        const int tile_no = pw * 64 / KvTraits<FMT>::TILE;
+        st.d[jj][0] = ldg16(row + 64 * blk + 16 * q);
+        const int tile_no = blk * 64 / KvTraits<FMT>::TILE;
         st.sc[jj] = __ldg(reinterpret_cast<const uint32_t*>(scl) + (tile_no >> 2));
       } else {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) st.d[jj][k] = ldg16(row + 128 * pw + 64 * half + 16 * k);
+        st.d[jj][0] = ldg16(row + 128 * blk + 32 * q);
+        st.d[jj][1] = ldg16(row + 128 * blk + 32 * q + 16);
       }
     }
-    if (S::HAS_LAST && j == pw) {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) st.last[k] = make_uint4(0, 0, 0, 0);
+    if (C::HAS_LAST && j == blk) {
+      st.last[0] = st.last[1] = make_uint4(0, 0, 0, 0);
       if (valid) {
-        const uint8_t* src = row + (C::PAGED ? C::NOPE_SEGS * 64 : S::MAIN_BLOCKS * 128) + 64 * half;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) st.last[k] = ldg16(src + 16 * k);
+        st.last[0] = ldg16(row + C::LAST_SRC_OFFSET + 32 * q);
+        st.last[1] = ldg16(row + C::LAST_SRC_OFFSET + 32 * q + 16);
       }
     }
   }
@@ -234,43 +245,32 @@ __device__ __forceinline__ void stage_load(Stage<FMT, DQK>& st, const AttnParams
 // Convert and store k-step j (held at register slot jj) into the swizzled K tile.
 template <int FMT, int DQK>
 __device__ __forceinline__ void stage_store(const Stage<FMT, DQK>& st, uint32_t sK, int j, int jj,
-                                            int pw, int lane) {
-  using S = Stage<FMT, DQK>;
+                                            int warp, int lane) {
   using C = Cfg<FMT, DQK>;
-  const int row_in = lane >> 1, half = lane & 1;
-  const int row = 16 * j + row_in, x = row_in & 7;
-  const uint32_t rbase = sK + row * 128;
-  if (pw < S::MAIN_BLOCKS) {
-    const uint32_t a = rbase + pw * KBLOCK_BYTES;
+  const int blk = warp & 7, rh = warp >> 3, r = lane >> 2, q = lane & 3;
+  const uint32_t rbase = sK + (16 * j + 8 * rh + r) * 128;      // (row & 7) == r
+  const uint32_t c0 = ((2 * q) ^ r) << 4, c1 = ((2 * q + 1) ^ r) << 4;
+  if (blk < C::MAIN_BLOCKS) {
+    const uint32_t a = rbase + blk * KBLOCK_BYTES;
     if constexpr (C::PAGED) {
-      const int tile_no = pw * 64 / KvTraits<FMT>::TILE;
+      const int tile_no = blk * 64 / KvTraits<FMT>::TILE;
       const ScaleMul mul = make_scale_mul((st.sc[jj] >> (8 * (tile_no & 3))) & 0xffu);
-      uint32_t o[16];
+      uint32_t o[8];
       dequant4_fast(st.d[jj][0].x, mul, o[0], o[1]);
       dequant4_fast(st.d[jj][0].y, mul, o[2], o[3]);
       dequant4_fast(st.d[jj][0].z, mul, o[4], o[5]);
       dequant4_fast(st.d[jj][0].w, mul, o[6], o[7]);
-      dequant4_fast(st.d[jj][1].x, mul, o[8], o[9]);
-      dequant4_fast(st.d[jj][1].y, mul, o[10], o[11]);
-      dequant4_fast(st.d[jj][1].z, mul, o[12], o[13]);
-      dequant4_fast(st.d[jj][1].w, mul, o[14], o[15]);
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        st_shared_v4(a + (((4 * half + k) ^ x) << 4), o[4 * k], o[4 * k + 1], o[4 * k + 2],
-                     o[4 * k + 3]);
+      st_shared_v4(a + c0, o[0], o[1], o[2], o[3]);
+      st_shared_v4(a + c1, o[4], o[5], o[6], o[7]);
     } else {
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        st_shared_v4(a + (((4 * half + k) ^ x) << 4), st.d[jj][k].x, st.d[jj][k].y, st.d[jj][k].z,
-                     st.d[jj][k].w);
+      st_shared_v4(a + c0, st.d[jj][0].x, st.d[jj][0].y, st.d[jj][0].z, st.d[jj][0].w);
+      st_shared_v4(a + c1, st.d[jj][1].x, st.d[jj][1].y, st.d[jj][1].z, st.d[jj][1].w);
     }
   }
-  if (S::HAS_LAST && j == pw) {
+  if (C::HAS_LAST && j == blk) {
     const uint32_t a = rbase + (C::NB - 1) * KBLOCK_BYTES;
-#pragma unroll
-    for (int k = 0; k < 4; ++k)
-      st_shared_v4(a + (((4 * half + k) ^ x) << 4), st.last[k].x, st.last[k].y, st.last[k].z,
-                   st.last[k].w);
+    st_shared_v4(a + c0, st.last[0].x, st.last[0].y, st.last[0].z, st.last[0].w);
+    st_shared_v4(a + c1, st.last[1].x, st.last[1].y, st.last[1].z, st.last[1].w);
   }
 }
 
@@ -299,8 +299,6 @@ sm100_attn_kernel(const AttnParams p) {
   const bool decode = p.mode == MODE_DECODE;
   const bool mask_invalid = !decode || (p.flags & DSV4_FLAG_MASK_INVALID);
   const bool split_out = p.n_splits > 1;
-  const bool is_producer = warp >= SOFTMAX_WARPS;
-  const int pw = warp - SOFTMAX_WARPS;
 
   ListView lv;
   int xlen;
@@ -341,31 +339,36 @@ sm100_attn_kernel(const AttnParams p) {
     return;
   }
 
-  // ---- set-up (run by every warp inside its own role branch, so that each role's
-  // register budget is in force before any of its long-lived values exist) ----------
-  auto cta_setup = [&]() {
-    if (tid == 0) {
-      mbar_init(smem_u32(&ctrl.k_full), PRODUCER_WARPS);
-      mbar_init(smem_u32(&ctrl.s_full), 1);
-      mbar_init(smem_u32(&ctrl.p_full), SOFTMAX_WARPS);
-      mbar_init(smem_u32(&ctrl.o_done), 1);
-      for (int i = 0; i < 8; ++i) mbar_init(smem_u32(&ctrl.kv_free[i]), 1);
-      ctrl.resc[0] = ctrl.resc[1] = 0;
-      ctrl.fail = 0;
-      mbar_init_fence();
-    }
-    if (tid < HEADS) {
-      ctrl.mref[tid] = -INFINITY;
-      ctrl.muse[tid] = 0.f;
-      ctrl.mtrue[tid] = -INFINITY;
-      ctrl.alpha[tid] = 1.f;
-    }
-    if (warp == 0) {
-      tmem_alloc(smem_u32(&ctrl.tmem), TMEM_COLS);
-      tmem_relinquish();
-    }
+  // The first tile's gather goes in flight before anything else.
+  S stage;
+  int tidx[KSTEPS];
+  index_load(tidx, lv, lv.begin, warp, lane);
+  stage_load(stage, p, lv, tidx, lv.begin, 0, warp, lane);
+
+  // ---- set-up: barriers, TMEM, Q ---------------------------------------------------
+  if (tid == 0) {
+    mbar_init(smem_u32(&ctrl.k_full), WARPS);
+    mbar_init(smem_u32(&ctrl.s_full), 1);
+    mbar_init(smem_u32(&ctrl.p_full), WARPS);
+    mbar_init(smem_u32(&ctrl.o_done), 1);
+    for (int i = 0; i < KSTEPS; ++i) mbar_init(smem_u32(&ctrl.kv_free[i]), 1);
+    ctrl.resc[0] = ctrl.resc[1] = 0;
+    ctrl.fail = 0;
+    mbar_init_fence();
+  }
+  if (tid < HEADS) {
+    ctrl.mref[tid] = -INFINITY;
+    ctrl.muse[tid] = 0.f;
+    ctrl.mtrue[tid] = -INFINITY;
+    ctrl.alpha[tid] = 1.f;
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&ctrl.tmem), TMEM_COLS);
+    tmem_relinquish();
+  }
+  {
     // Q[head][d] -> blocks [d/64][head][64], 128-byte swizzle; absent heads are zero.
-    // Loads are issued in batches so their latencies overlap.
+    // Loads are issued three at a time so their latencies overlap.
     const __nv_bfloat16* qrow0 = p.q + bi * p.stride_q_b + si * p.stride_q_s + head0 * p.stride_q_h;
     constexpr int Q_CHUNKS = HEADS * C::NB * 8;
     constexpr int Q_BATCH = 3;
@@ -390,20 +393,21 @@ sm100_attn_kernel(const AttnParams p) {
                        qv[it].z, qv[it].w);
       }
     }
-    fence_async_smem();
-    tc_fence_before_sync();
-    bar_sync(3, THREADS);
-    tc_fence_after_sync();
-    if (tid == 0) stamp(p, 1);
-  };
+  }
+  fence_async_smem();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = ctrl.tmem;
+  if (tid == 0) stamp(p, 1);
 #define TSTAMP(t, k) do { if ((t) < PROF_MAX_TILES) stamp(p, PROF_TILE0 + (t) * PROF_PER_TILE + (k)); } while (0)
 
   const uint32_t bar_k_full = smem_u32(&ctrl.k_full), bar_s_full = smem_u32(&ctrl.s_full);
   const uint32_t bar_p_full = smem_u32(&ctrl.p_full), bar_o_done = smem_u32(&ctrl.o_done);
   const uint32_t bar_kv_free0 = smem_u32(&ctrl.kv_free[0]);
+  bool ok = true;      // false once one of this thread's bounded waits has given up
 
-  // ---- MMA issue: done by thread 0 (lane 0 of softmax warp 0), in between its softmax
-  // steps; the tensor core runs asynchronously and reports through mbarriers ---------
+  // ---- MMA issue (thread 0 only) -----------------------------------------------------
   const uint32_t idesc_qk = make_idesc_bf16(TILE, HEADS, 0, 0);
   const uint32_t idesc_pv = make_idesc_bf16(128, HEADS, 1, 1);
   const uint64_t dK = make_smem_desc(sK, 16, 1024, SWZ_128B);            // K-major view
@@ -414,263 +418,247 @@ sm100_attn_kernel(const AttnParams p) {
   const uint32_t dQ_lo = static_cast<uint32_t>(dQ), dQ_hi = static_cast<uint32_t>(dQ >> 32);
   const uint32_t dV_lo = static_cast<uint32_t>(dV), dV_hi = static_cast<uint32_t>(dV >> 32);
   const uint32_t dP_lo = static_cast<uint32_t>(dP), dP_hi = static_cast<uint32_t>(dP >> 32);
-  auto issue_qk = [&](uint32_t tmem, int t) -> bool {
-    if (!mbar_wait(bar_k_full, t & 1)) { atomicExch(&g_attn_error, ERR_KFULL); return false; }
+  auto issue_qk = [&](int t, bool& ok) {
+    if (ok && !mbar_wait(bar_k_full, t & 1)) { atomicExch(&g_attn_error, ERR_KFULL); ok = false; }
     tc_fence_after_sync();
     TSTAMP(t, 1);
-#pragma unroll
+#pragma unroll 1
     for (int kb = 0; kb < C::NB; ++kb) {
+      const uint32_t a = dK_lo + ((kb * KBLOCK_BYTES) >> 4), b = dQ_lo + ((kb * QBLOCK_BYTES) >> 4);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
-        umma_bf16_lohi(tmem + COL_S, dK_lo + ((kb * KBLOCK_BYTES + ks * 32) >> 4), dK_hi,
-                       dQ_lo + ((kb * QBLOCK_BYTES + ks * 32) >> 4), dQ_hi, idesc_qk,
-                       (kb | ks) != 0);
+        umma_bf16_lohi(tmem + COL_S, a + 2 * ks, dK_hi, b + 2 * ks, dQ_hi, idesc_qk, (kb | ks) != 0);
     }
     umma_commit(bar_s_full);
-    return true;
   };
-  auto issue_pv = [&](uint32_t tmem, int t, bool last) -> bool {
-    if (!mbar_wait(bar_p_full, t & 1)) { atomicExch(&g_attn_error, ERR_PFULL); return false; }
+  auto issue_pv = [&](int t, bool last, bool& ok) {
+    if (ok && !mbar_wait(bar_p_full, t & 1)) { atomicExch(&g_attn_error, ERR_PFULL); ok = false; }
     tc_fence_after_sync();
     TSTAMP(t, 5);
-#pragma unroll
-    for (int j = 0; j < TILE / 16; ++j) {
+#pragma unroll 1
+    for (int j = 0; j < KSTEPS; ++j) {
+      const uint32_t a = dV_lo + ((j * 2048) >> 4), b = dP_lo + ((j * 2048) >> 4);
 #pragma unroll
       for (int m = 0; m < D_V / 128; ++m)
-        umma_bf16_lohi(tmem + COL_O + m * HEADS, dV_lo + ((m * 2 * KBLOCK_BYTES + j * 2048) >> 4),
-                       dV_hi, dP_lo + ((j * 2048) >> 4), dP_hi, idesc_pv, (t | j) != 0);
+        umma_bf16_lohi(tmem + COL_O + m * HEADS, a + ((m * 2 * KBLOCK_BYTES) >> 4), dV_hi, b, dP_hi,
+                       idesc_pv, (t | j) != 0);
       umma_commit(bar_kv_free0 + 8 * j);
     }
     if (last) umma_commit(bar_o_done);
-    return true;
   };
 
-  uint32_t tmem;
-  if (is_producer) {
-    // =========================== producers ==========================================
-    S stage;
-    stage_load(stage, p, lv, lv.begin, 0, pw, lane);   // first gather in flight before set-up
-    cta_setup();
-    tmem = ctrl.tmem;
-    bool ok = true;
-    for (int t = 0; t < n_tiles && ok; ++t) {
-      const int j0 = lv.begin + t * TILE;
+  // ---- refill of the K tile from the staged registers -------------------------------
+  // `wait_tile` >= 0: rows of k-step j may be overwritten only once the P.V step j of
+  // that tile has retired.  After a wait has given up (`ok` false) no further wait is
+  // attempted, but every thread keeps walking the same path so that the CTA-wide
+  // barriers below stay matched; the outputs are then suppressed.
+  auto refill = [&](int j0, int wait_tile, bool& ok) {
 #pragma unroll
-      for (int ph = 0; ph < S::PHASES; ++ph) {
-        if (ph > 0) stage_load(stage, p, lv, j0, ph, pw, lane);
+    for (int ph = 0; ph < S::PHASES; ++ph) {
+      if (ph > 0) stage_load(stage, p, lv, tidx, j0, ph, warp, lane);
 #pragma unroll
-        for (int jj = 0; jj < S::KS; ++jj) {
-          const int j = ph * S::KS + jj;
-          if (t > 0 && ok && !mbar_wait_warp(bar_kv_free0 + 8 * j, (t - 1) & 1, lane)) {
-            atomicExch(&g_attn_error, ERR_KVFREE);
-            ok = false;
-          }
-          if (pw == 0 && lane == 0 && jj == 0 && ph == 0) TSTAMP(t, 6);
-          if (ok) stage_store(stage, sK, j, jj, pw, lane);
+      for (int jj = 0; jj < S::KS; ++jj) {
+        const int j = ph * S::KS + jj;
+        if (wait_tile >= 0 && ok && !mbar_wait_warp(bar_kv_free0 + 8 * j, wait_tile & 1, lane)) {
+          atomicExch(&g_attn_error, ERR_KVFREE);
+          ok = false;
         }
+        stage_store(stage, sK, j, jj, warp, lane);
       }
-      if (!ok) break;
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_k_full);
-      if (pw == 0 && lane == 0) TSTAMP(t, 0);
-      if (pw == PRODUCER_WARPS - 1 && lane == 0) TSTAMP(t, 7);
-      if (t + 1 < n_tiles) stage_load(stage, p, lv, j0 + TILE, 0, pw, lane);
     }
-  } else {
-    // =========================== softmax ============================================
-    // Warp (lg, ch): TMEM lanes 32*lg.. (tile rows), head columns 32*ch..32*ch+31.
-    cta_setup();
-    tmem = ctrl.tmem;
-    const int lg = warp & 3, ch = warp >> 2;
-    const int row = lg * 32 + lane;
-    const uint32_t tlane = static_cast<uint32_t>(lg * 32) << 16;
-    const float cs = p.sm_scale * LOG2E;
-    float lsum[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) lsum[i] = 0.f;
-    bool ok = true;
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_k_full);
+  };
 
-    for (int t = 0; t < n_tiles; ++t) {
-      // Is this row masked (beyond the range, or an invalid index under masking rules)?
-      bool masked = true;
-      {
-        const int j = lv.begin + t * TILE + row;
-        if (j < lv.end) {
-          int idx;
-          bool is_main;
-          const bool valid = list_entry(p, lv, j, idx, is_main);
-          masked = !valid && mask_invalid;
-        }
-      }
-      if (tid == 0) issue_qk(tmem, t);
-      __syncwarp();
-      if (!mbar_wait_warp(bar_s_full, t & 1, lane)) { atomicExch(&g_attn_error, ERR_SFULL); ok = false; break; }
-      tc_fence_after_sync();
-      if (tid == 0) TSTAMP(t, 2);
+  // Softmax geometry: TMEM lanes 32*lg.. (tile rows), head columns 16*cg..16*cg+15.
+  const int lg = warp & 3, cg = warp >> 2;
+  const int row = lg * 32 + lane;
+  const uint32_t tlane = static_cast<uint32_t>(lg * 32) << 16;
+  const float cs = p.sm_scale * LOG2E;
+  float lsum[COLS_PER_WARP];
+#pragma unroll
+  for (int i = 0; i < COLS_PER_WARP; ++i) lsum[i] = 0.f;
 
-      // pass 1: per-head max over the tile's rows
-      {
-        float v[32];
-        uint32_t ra[16], rb[16];
-        tmem_ld16(tmem + tlane + COL_S + ch * 32, ra);
-        tmem_ld16(tmem + tlane + COL_S + ch * 32 + 16, rb);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          v[i] = masked ? -INFINITY : __uint_as_float(ra[i]);
-          v[16 + i] = masked ? -INFINITY : __uint_as_float(rb[i]);
-        }
-        ctrl.wred[lg][ch * 32 + lane] = warp_col_reduce32<true>(v, lane);
-      }
-      bar_sync(1, SOFTMAX_WARPS * 32);
-      if (tid < HEADS) {
-        float tm = fmaxf(fmaxf(ctrl.wred[0][tid], ctrl.wred[1][tid]),
-                         fmaxf(ctrl.wred[2][tid], ctrl.wred[3][tid])) * cs;
-        ctrl.mtrue[tid] = fmaxf(ctrl.mtrue[tid], tm);
-        const float mr = ctrl.mref[tid];
-        float alpha = 1.f;
-        if (tm > mr + RESCALE_THRESHOLD) {                 // also the first finite max
-          alpha = (mr == -INFINITY) ? 0.f : ex2(mr - tm);
-          ctrl.mref[tid] = tm;
-          ctrl.muse[tid] = tm;
-          ctrl.resc[t & 1] = 1;
-        }
-        ctrl.alpha[tid] = alpha;
-      }
-      if (tid == 64) ctrl.resc[(t + 1) & 1] = 0;
-      bar_sync(1, SOFTMAX_WARPS * 32);
-      if (tid == 0) TSTAMP(t, 3);
+  if (tid == 0) TSTAMP(0, 6);
+  refill(lv.begin, -1, ok);
+  if (tid == 0) TSTAMP(0, 0);
+  if (n_tiles > 1) index_load(tidx, lv, lv.begin + TILE, warp, lane);
 
-      if (ctrl.resc[t & 1]) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) lsum[i] *= ctrl.alpha[ch * 32 + i];
-        if (t > 0) {
-          // this warp rescales O^T slices 2*ch and 2*ch+1 for its 32 TMEM lanes
-#pragma unroll 1
-          for (int c = 0; c < 2 * (HEADS / 16); ++c) {
-            const int m = 2 * ch + c / (HEADS / 16), c4 = c % (HEADS / 16);
-            uint32_t o[16];
-            const uint32_t addr = tmem + tlane + COL_O + m * HEADS + c4 * 16;
-            tmem_ld16(addr, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              o[i] = __float_as_uint(__uint_as_float(o[i]) * ctrl.alpha[c4 * 16 + i]);
-            tmem_st16(addr, o);
-          }
-          tmem_st_wait();
-        }
-      }
-
-      // pass 2: p = 2^(s*c - mref), denominators, this warp's half of the P^T row
-      {
-        const uint32_t prow = sP + row * 128;
-        const int x = row & 7;
-        // TMEM loads are warp-collective: every lane takes part even if its row is masked.
-        uint32_t sa[16], sb[16];
-        tmem_ld16(tmem + tlane + COL_S + ch * 32, sa);
-        tmem_ld16(tmem + tlane + COL_S + ch * 32 + 16, sb);
-        tmem_ld_wait();
-        if (__any_sync(0xffffffffu, masked)) {          // rare: ragged tile or masked entries
-          const uint32_t ninf = __float_as_uint(-INFINITY);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            sa[i] = masked ? ninf : sa[i];
-            sb[i] = masked ? ninf : sb[i];
-          }
-        }
-        uint32_t pk[16];
-#pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          const float4 mu = *reinterpret_cast<const float4*>(&ctrl.muse[ch * 32 + q4 * 4]);
-          const uint32_t* src = q4 < 4 ? &sa[q4 * 4] : &sb[(q4 - 4) * 4];
-          const float p0 = ex2(fmaf(__uint_as_float(src[0]), cs, -mu.x));
-          const float p1 = ex2(fmaf(__uint_as_float(src[1]), cs, -mu.y));
-          const float p2 = ex2(fmaf(__uint_as_float(src[2]), cs, -mu.z));
-          const float p3 = ex2(fmaf(__uint_as_float(src[3]), cs, -mu.w));
-          lsum[q4 * 4 + 0] += p0;
-          lsum[q4 * 4 + 1] += p1;
-          lsum[q4 * 4 + 2] += p2;
-          lsum[q4 * 4 + 3] += p3;
-          __nv_bfloat162 a = __floats2bfloat162_rn(p0, p1), b = __floats2bfloat162_rn(p2, p3);
-          pk[q4 * 2] = *reinterpret_cast<uint32_t*>(&a);
-          pk[q4 * 2 + 1] = *reinterpret_cast<uint32_t*>(&b);
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          st_shared_v4(prow + (((4 * ch + k) ^ x) << 4), pk[4 * k], pk[4 * k + 1], pk[4 * k + 2],
-                       pk[4 * k + 3]);
-      }
-      fence_async_smem();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p_full);
-      if (tid == 0) {
-        TSTAMP(t, 4);
-        issue_pv(tmem, t, t + 1 == n_tiles);
-      }
-      __syncwarp();
-    }
-
-    // ---- final denominators and output factors -------------------------------------
-    if (ok && !mbar_wait_warp(bar_o_done, 0, lane)) { atomicExch(&g_attn_error, ERR_ODONE); ok = false; }
-    tc_fence_after_sync();
-    if (tid == 0) stamp(p, 3);
-    if (!ok) ctrl.fail = 1;
+  for (int t = 0; t < n_tiles; ++t) {
+    // Is this thread's row masked (beyond the range, or an invalid entry under masking rules)?
+    bool masked = true;
     {
-      float v[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = lsum[i];
-      ctrl.wred[lg][ch * 32 + lane] = warp_col_reduce32<false>(v, lane);
-    }
-    bar_sync(1, SOFTMAX_WARPS * 32);
-    if (tid < HEADS && !ctrl.fail) {
-      const float l = ctrl.wred[0][tid] + ctrl.wred[1][tid] + ctrl.wred[2][tid] + ctrl.wred[3][tid];
-      const float mr = ctrl.mref[tid];
-      float f;
-      if (split_out) {
-        const bool empty = !(l > 0.f);
-        f = empty ? 0.f : 1.f / l;
-        if (tid < heads_here) p.lse_accum[acc_slot0 + tid] = empty ? -INFINITY : logf(l) + mr * LN2;
-      } else {
-        const bool has_sink = p.sink != nullptr;
-        float lse_v, ml_v;
-        f = finalize_row(p.mode, mr == -INFINITY ? -INFINITY : mr * LN2, l, has_sink,
-                         (has_sink && tid < heads_here) ? p.sink[head0 + tid] : 0.f, lse_v, ml_v);
-        if (tid < heads_here) {
-          p.lse[bi * p.stride_lse_b + si * p.stride_lse_s + (head0 + tid) * p.stride_lse_h] = lse_v;
-          if (p.max_logits)
-            p.max_logits[bi * p.stride_ml_b + head0 + tid] =
-                (ml_v == -INFINITY) ? -INFINITY : ctrl.mtrue[tid] * LN2;
-        }
+      const int j = lv.begin + t * TILE + row;
+      if (j < lv.end) {
+        const int idx = list_index(lv, j);
+        const int ntok = (j < lv.len) ? p.n_tok : p.extra_n_tok;
+        masked = !(idx >= 0 && idx < ntok) && mask_invalid;
       }
-      ctrl.alpha[tid] = f;
+    }
+    if (tid == 0) issue_qk(t, ok);
+    __syncwarp();
+    const bool more = t + 1 < n_tiles;
+    if (more) stage_load(stage, p, lv, tidx, lv.begin + (t + 1) * TILE, 0, warp, lane);
+    if (tid == 0 && t > 0) TSTAMP(t, 6);
+
+    if (ok && !mbar_wait_warp(bar_s_full, t & 1, lane)) { atomicExch(&g_attn_error, ERR_SFULL); ok = false; }
+    tc_fence_after_sync();
+    if (tid == 0) TSTAMP(t, 2);
+
+    // pass 1: per-head max over the tile's rows
+    {
+      float v[16];
+      uint32_t ra[16];
+      tmem_ld16(tmem + tlane + COL_S + cg * 16, ra);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = masked ? -INFINITY : __uint_as_float(ra[i]);
+      const float cm = warp_col_reduce16<true>(v, lane);
+      if (lane < 16) ctrl.wred[lg][cg * 16 + lane] = cm;
+    }
+    __syncthreads();
+    if (tid < HEADS) {
+      float tm = fmaxf(fmaxf(ctrl.wred[0][tid], ctrl.wred[1][tid]),
+                       fmaxf(ctrl.wred[2][tid], ctrl.wred[3][tid])) * cs;
+      ctrl.mtrue[tid] = fmaxf(ctrl.mtrue[tid], tm);
+      const float mr = ctrl.mref[tid];
+      float alpha = 1.f;
+      if (tm > mr + RESCALE_THRESHOLD) {                 // also the first finite max
+        alpha = (mr == -INFINITY) ? 0.f : ex2(mr - tm);
+        ctrl.mref[tid] = tm;
+        ctrl.muse[tid] = tm;
+        ctrl.resc[t & 1] = 1;
+      }
+      ctrl.alpha[tid] = alpha;
+    }
+    if (tid == 64) ctrl.resc[(t + 1) & 1] = 0;
+    __syncthreads();
+    if (tid == 0) TSTAMP(t, 3);
+
+    if (ctrl.resc[t & 1]) {
+#pragma unroll
+      for (int i = 0; i < COLS_PER_WARP; ++i) lsum[i] *= ctrl.alpha[cg * 16 + i];
+      if (t > 0) {
+        // this warp rescales slice cg of O^T for its 32 TMEM lanes
+#pragma unroll 1
+        for (int c4 = 0; c4 < HEADS / 16; ++c4) {
+          uint32_t o[16];
+          const uint32_t addr = tmem + tlane + COL_O + cg * HEADS + c4 * 16;
+          tmem_ld16(addr, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            o[i] = __float_as_uint(__uint_as_float(o[i]) * ctrl.alpha[c4 * 16 + i]);
+          tmem_st16(addr, o);
+        }
+        tmem_st_wait();
+      }
+    }
+
+    // pass 2: p = 2^(s*c - mref), denominators, this thread's 32 bytes of the P^T row
+    {
+      uint32_t s[16];
+      tmem_ld16(tmem + tlane + COL_S + cg * 16, s);   // warp-collective: all lanes take part
+      tmem_ld_wait();
+      if (__any_sync(0xffffffffu, masked)) {          // rare: ragged tile or masked entries
+        const uint32_t ninf = __float_as_uint(-INFINITY);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) s[i] = masked ? ninf : s[i];
+      }
+      uint32_t pk[8];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const float4 mu = *reinterpret_cast<const float4*>(&ctrl.muse[cg * 16 + q4 * 4]);
+        const float p0 = ex2(fmaf(__uint_as_float(s[q4 * 4 + 0]), cs, -mu.x));
+        const float p1 = ex2(fmaf(__uint_as_float(s[q4 * 4 + 1]), cs, -mu.y));
+        const float p2 = ex2(fmaf(__uint_as_float(s[q4 * 4 + 2]), cs, -mu.z));
+        const float p3 = ex2(fmaf(__uint_as_float(s[q4 * 4 + 3]), cs, -mu.w));
+        lsum[q4 * 4 + 0] += p0;
+        lsum[q4 * 4 + 1] += p1;
+        lsum[q4 * 4 + 2] += p2;
+        lsum[q4 * 4 + 3] += p3;
+        __nv_bfloat162 a = __floats2bfloat162_rn(p0, p1), b = __floats2bfloat162_rn(p2, p3);
+        pk[q4 * 2] = *reinterpret_cast<uint32_t*>(&a);
+        pk[q4 * 2 + 1] = *reinterpret_cast<uint32_t*>(&b);
+      }
+      const uint32_t prow = sP + row * 128;
+      const int x = row & 7;
+      st_shared_v4(prow + (((2 * cg) ^ x) << 4), pk[0], pk[1], pk[2], pk[3]);
+      st_shared_v4(prow + (((2 * cg + 1) ^ x) << 4), pk[4], pk[5], pk[6], pk[7]);
+    }
+    fence_async_smem();
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_p_full);
+    if (tid == 0) {
+      TSTAMP(t, 4);
+      issue_pv(t, !more, ok);
+    }
+    __syncwarp();
+
+    // refill the tile behind the P.V product
+    if (more) {
+      refill(lv.begin + (t + 1) * TILE, t, ok);
+      if (t + 2 < n_tiles) index_load(tidx, lv, lv.begin + (t + 2) * TILE, warp, lane);
+      if (tid == 0) TSTAMP(t + 1, 0);
+      if (tid == THREADS - 32) TSTAMP(t + 1, 7);
     }
   }
 
-  // ---- epilogue: all 16 softmax + producer warps drain O^T -------------------------
+  // ---- final denominators and output factors ---------------------------------------
+  if (ok && !mbar_wait_warp(bar_o_done, 0, lane)) { atomicExch(&g_attn_error, ERR_ODONE); ok = false; }
+  tc_fence_after_sync();
+  if (tid == 0) stamp(p, 3);
+  if (!ok) ctrl.fail = 1;
   {
-    bar_sync(2, THREADS);
-    tc_fence_after_sync();
-    if (!ctrl.fail) {
-      // warp w: O^T slice m = w / 4, TMEM lanes 32 * (w % 4)..; d = 128 m + lane offset.
-      const int m = warp >> 2, lg = warp & 3;
-      const uint32_t tl = static_cast<uint32_t>(lg * 32) << 16;
-      const int d = m * 128 + lg * 32 + lane;
+    float v[16];
 #pragma unroll
-      for (int c4 = 0; c4 < HEADS / 16; ++c4) {
-        uint32_t o[16];
-        tmem_ld16(tmem + tl + COL_O + m * HEADS + c4 * 16, o);
-        tmem_ld_wait();
+    for (int i = 0; i < 16; ++i) v[i] = lsum[i];
+    const float cm = warp_col_reduce16<false>(v, lane);
+    if (lane < 16) ctrl.wred[lg][cg * 16 + lane] = cm;
+  }
+  __syncthreads();
+  if (tid < HEADS && !ctrl.fail) {
+    const float l = ctrl.wred[0][tid] + ctrl.wred[1][tid] + ctrl.wred[2][tid] + ctrl.wred[3][tid];
+    const float mr = ctrl.mref[tid];
+    float f;
+    if (split_out) {
+      const bool empty = !(l > 0.f);
+      f = empty ? 0.f : 1.f / l;
+      if (tid < heads_here) p.lse_accum[acc_slot0 + tid] = empty ? -INFINITY : logf(l) + mr * LN2;
+    } else {
+      const bool has_sink = p.sink != nullptr;
+      float lse_v, ml_v;
+      f = finalize_row(p.mode, mr == -INFINITY ? -INFINITY : mr * LN2, l, has_sink,
+                       (has_sink && tid < heads_here) ? p.sink[head0 + tid] : 0.f, lse_v, ml_v);
+      if (tid < heads_here) {
+        p.lse[bi * p.stride_lse_b + si * p.stride_lse_s + (head0 + tid) * p.stride_lse_h] = lse_v;
+        if (p.max_logits)
+          p.max_logits[bi * p.stride_ml_b + head0 + tid] =
+              (ml_v == -INFINITY) ? -INFINITY : ctrl.mtrue[tid] * LN2;
+      }
+    }
+    ctrl.alpha[tid] = f;
+  }
+  __syncthreads();
+
+  // ---- epilogue: warp w drains O^T slice w / 4 for TMEM lanes 32 * (w % 4).. --------
+  if (!ctrl.fail) {
+    const int m = warp >> 2;
+    const int d = m * 128 + lg * 32 + lane;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int h = c4 * 16 + i;
-          if (h < heads_here) {
-            const float val = __uint_as_float(o[i]) * ctrl.alpha[h];
-            if (split_out) p.o_accum[(acc_slot0 + h) * D_V + d] = val;
-            else out_base[h * p.stride_o_h + d] = __float2bfloat16_rn(val);
-          }
+    for (int c4 = 0; c4 < HEADS / 16; ++c4) {
+      uint32_t o[16];
+      tmem_ld16(tmem + tlane + COL_O + m * HEADS + c4 * 16, o);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int h = c4 * 16 + i;
+        if (h < heads_here) {
+          const float val = __uint_as_float(o[i]) * ctrl.alpha[h];
+          if (split_out) p.o_accum[(acc_slot0 + h) * D_V + d] = val;
+          else out_base[h * p.stride_o_h + d] = __float2bfloat16_rn(val);
         }
       }
     }
