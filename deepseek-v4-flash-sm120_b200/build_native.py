@@ -37,6 +37,8 @@ def build(verbose: bool = False, force: bool = False) -> str:
            "--threads", "4"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
+    if os.environ.get("DSV4_EXTRA_DEFINES"):
+        cmd += ["-D" + d for d in os.environ["DSV4_EXTRA_DEFINES"].split(",")]
     if os.environ.get("DSV4_KERNEL_DEBUG"):
         cmd += ["-DDSV4_DEBUG=1"]
     cmd += [os.path.join(CSRC, s) for s in SOURCES] + ["-o", OUT]

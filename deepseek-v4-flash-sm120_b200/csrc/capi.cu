@@ -54,11 +54,10 @@ int current_device_is_sm100() {
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int check_paged(int kv_format, int d_qk, int page_block, int64_t stride_block, const void* kv) {
-  int row_bytes, per_tok;
-  if (kv_format == DSV4_KV_MODEL1) { row_bytes = 576; per_tok = 584; if (d_qk != 512) return DSV4_ERR_LAYOUT; }
-  else if (kv_format == DSV4_KV_V32) { row_bytes = 640; per_tok = 644; if (d_qk != 576) return DSV4_ERR_LAYOUT; }
+  int per_tok;
+  if (kv_format == DSV4_KV_MODEL1) { per_tok = 584; if (d_qk != 512) return DSV4_ERR_LAYOUT; }
+  else if (kv_format == DSV4_KV_V32) { per_tok = 644; if (d_qk != 576) return DSV4_ERR_LAYOUT; }
   else return DSV4_ERR_LAYOUT;
-  (void)row_bytes;
   if (page_block < 1) return DSV4_ERR_SHAPE;
   if (stride_block < static_cast<int64_t>(page_block) * per_tok) return DSV4_ERR_LAYOUT;
   if ((stride_block & 15) || !aligned16(kv)) return DSV4_ERR_ALIGN;

@@ -102,6 +102,15 @@ __device__ __forceinline__ void dequant4_fast(uint32_t w, const ScaleMul& m, uin
   hi = x1;
 }
 
+// Hot-path variant for the common case of a single multiplier (ScaleMul::c2 == 0).
+__device__ __forceinline__ void dequant4_one_mul(uint32_t w, uint32_t c1, uint32_t& lo,
+                                                 uint32_t& hi) {
+  const uint32_t t0 = __byte_perm(w, 0u, 0x1404);     // [0, b0, 0, b1]
+  const uint32_t t1 = __byte_perm(w, 0u, 0x3424);     // [0, b2, 0, b3]
+  lo = bf16x2_mul((t0 & 0x80008000u) | ((t0 >> 4) & 0x07F007F0u), c1);
+  hi = bf16x2_mul((t1 & 0x80008000u) | ((t1 >> 4) & 0x07F007F0u), c1);
+}
+
 // The same through fp32 arithmetic (no dependence on packed-BF16 subnormal
 // handling); kept as a cross-check of dequant4_fast.
 __device__ __forceinline__ void dequant4_f32(uint32_t w, uint32_t s, uint32_t& lo, uint32_t& hi) {

@@ -49,8 +49,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uin
 // with a time hint was observed to sleep for the whole hint).  Gives up after
 // `limit` probes (roughly a tenth of a second) and returns false, so that a
 // protocol error ends the kernel with a status code instead of a hang.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          uint32_t limit = (1u << 21)) {
+static __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = (1u << 21)) {
   for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_test(bar, parity)) return true;
     if (i > 8) __nanosleep(20);
@@ -61,7 +60,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
 // of waiters on shared memory at one per warp.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int lane) {
   uint32_t ok = 1;
-  if (lane == 0) ok = mbar_wait(bar, parity) ? 1u : 0u;
+  if (lane == 0) ok = (mbar_test(bar, parity) || mbar_wait(bar, parity)) ? 1u : 0u;
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
@@ -117,6 +116,34 @@ __device__ __forceinline__ void umma_bf16_lohi(uint32_t tmem_d, uint32_t a_lo, u
       "setp.ne.b32 p, %6, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
       ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Four MMAs in one go: descriptor start addresses a_lo + i * a_step, b_lo + i * b_step
+// (steps in 16-byte units), destinations tmem_d + i * d_step columns.  The first one
+// accumulates only if `acc_first` is non-zero; the rest accumulate iff `acc_rest`.
+// One predicate set-up and three instructions per MMA keep the issuing thread fast.
+__device__ __forceinline__ void umma_bf16_x4(uint32_t tmem_d, uint32_t d_step, uint32_t a_lo,
+                                             uint32_t a_hi, uint32_t a_step, uint32_t b_lo,
+                                             uint32_t b_hi, uint32_t b_step, uint32_t idesc,
+                                             uint32_t acc_first, uint32_t acc_rest) {
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t.reg .b64 da, db;\n\t.reg .b32 ta, tb, td;\n\t"
+      "setp.ne.b32 p0, %9, 0;\n\t"
+      "setp.ne.b32 p1, %10, 0;\n\t"
+      "mov.b64 da, {%2, %3};\n\t"
+      "mov.b64 db, {%5, %6};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %8, p0;\n\t"
+      "add.u32 ta, %2, %4;\n\t add.u32 tb, %5, %7;\n\t add.u32 td, %0, %1;\n\t"
+      "mov.b64 da, {ta, %3};\n\t mov.b64 db, {tb, %6};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [td], da, db, %8, p1;\n\t"
+      "add.u32 ta, ta, %4;\n\t add.u32 tb, tb, %7;\n\t add.u32 td, td, %1;\n\t"
+      "mov.b64 da, {ta, %3};\n\t mov.b64 db, {tb, %6};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [td], da, db, %8, p1;\n\t"
+      "add.u32 ta, ta, %4;\n\t add.u32 tb, tb, %7;\n\t add.u32 td, td, %1;\n\t"
+      "mov.b64 da, {ta, %3};\n\t mov.b64 db, {tb, %6};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [td], da, db, %8, p1;\n\t}"
+      ::"r"(tmem_d), "r"(d_step), "r"(a_lo), "r"(a_hi), "r"(a_step), "r"(b_lo), "r"(b_hi),
+        "r"(b_step), "r"(idesc), "r"(acc_first), "r"(acc_rest)
       : "memory");
 }
 // Arrive on an mbarrier once all MMAs issued so far by this thread complete.
@@ -181,6 +208,13 @@ __device__ __forceinline__ void tmem_ld_wait() {
 }
 __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Maximum of a float over the 32 lanes of the warp, returned to every lane.
+__device__ __forceinline__ float warp_max_f32(float v) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
 }
 
 __device__ __forceinline__ uint32_t elect_one() {

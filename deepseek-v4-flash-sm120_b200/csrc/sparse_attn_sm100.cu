@@ -13,10 +13,11 @@
 // (contraction over d) for the first product and as MN-major (contraction over
 // tokens) for the second.  With d_qk = 576 the tile (144 KB) and Q (72 KB) leave
 // no room for a second tile or a staging ring, so gathered rows are staged in
-// REGISTERS: every warp owns one 64-column block of 8 rows of each 16-row
-// "k-step" of the tile, issues the 16-byte loads of the next tile while the
-// current one is being multiplied, and writes each k-step (dequantised to BF16)
-// as soon as the P.V MMA step that last read those 16 rows has retired.  P^T
+// REGISTERS: the tile is cut into units of four rows x one 128-byte line dealt
+// round-robin to the warps; a warp issues the 16-byte loads of the next tile
+// while the current one is being multiplied, and writes each 16-row "k-step"
+// (dequantised to BF16) as soon as the P.V MMA step that last read those rows
+// has retired.  P^T
 // (16 KB) reuses the RoPE block of the tile, which only Q.K^T reads, when
 // d_qk = 576.
 //
@@ -68,11 +69,6 @@ template <int FMT, int DQK> struct Cfg {
   static constexpr int K_BYTES = NB * KBLOCK_BYTES;
   static constexpr int Q_BYTES = NB * QBLOCK_BYTES;
   static constexpr int P_BYTES = P_ALIAS ? 0 : TILE * 128;
-  // Blocks handled warp-per-block (8 warps x 2 row halves); a 9th block, if any
-  // (RoPE of the paged layouts, columns 512..575 of flat BF16), is handled per k-step.
-  static constexpr int MAIN_BLOCKS = PAGED ? NOPE_SEGS : (DQK == 576 ? 8 : NB);
-  static constexpr bool HAS_LAST = PAGED || DQK == 576;
-  static constexpr int LAST_SRC_OFFSET = PAGED ? NOPE_SEGS * 64 : MAIN_BLOCKS * 128;
 };
 
 struct Ctrl {
@@ -86,6 +82,7 @@ struct Ctrl {
   float muse[HEADS];                   // mref with -inf replaced by 0 (exponent offset)
   float mtrue[HEADS];                  // true running max, log2-scaled units
   float alpha[HEADS];                  // rescale factor / final output factor
+  uint32_t sc_tab[2][TILE * 2];        // per-tile scale words of the tile rows (double-buffered)
 };
 
 template <int FMT, int DQK>
@@ -155,122 +152,163 @@ __device__ __forceinline__ int list_index(const ListView& lv, int j) {
 
 // ---------------------------------------------------------------------------
 // Register staging of one tile.  A tile is 8 "k-steps" of 16 rows (the rows one
-// P.V MMA step contracts over).  Warp w owns column block w & 7 (64 values) of
-// rows 8 * (w >> 3) .. +8 of EVERY k-step: lane l holds a quarter of a block row
-// (row l >> 2, quarter l & 3: 16 FP8 bytes or 16 BF16 values).  When P.V retires
-// k-step j all sixteen warps refill those 16 rows at once, so the refill of the
-// tile trails the product by one k-step.  The 9th block of k-step j, if the
-// layout has one, is handled by the two warps whose block number is j.
-// Flat BF16 rows are twice as wide, so they are staged half a tile at a time.
+// P.V MMA step contracts over).  The unit of gather work is one 128-byte line of
+// four rows: 8 lanes x 16 bytes cover the line of a row, so a warp-wide load
+// touches four cache lines (a gather's cost in the L1 is per line touched).
+// Units are numbered k-step-major and dealt round-robin to the 16 warps, so that
+// when P.V retires k-step j all warps refill those 16 rows together and the
+// refill of the tile trails the product by one k-step.
+//   paged layouts: a row is CH 16-byte chunks: FP8 chunks (16 values -> two BF16
+//                  chunks of block chunk/4) then 8 RoPE chunks (copied to the last block);
+//   flat BF16:     a row is d_qk/8 chunks copied as they are; rows are twice as wide,
+//                  so they are staged half a tile at a time.
+// Scale bytes come from a per-tile table in shared memory (one load per row).
 // ---------------------------------------------------------------------------
 template <int FMT, int DQK> struct Stage {
   using C = Cfg<FMT, DQK>;
-  static constexpr int NV = C::PAGED ? 1 : 2;             // uint4 per lane per k-step
+  static constexpr int CH = C::PAGED ? C::NOPE_SEGS * 4 + 8 : DQK / 8;   // 16-byte chunks per row
+  static constexpr int FP8_CH = C::PAGED ? C::NOPE_SEGS * 4 : 0;
+  static constexpr int LINES = (CH + 7) / 8;
+  static constexpr int UNITS_PER_KSTEP = 4 * LINES;
+  static constexpr int PER_WARP = KSTEPS * UNITS_PER_KSTEP / WARPS;      // 10, 16 or 18
   static constexpr int PHASES = C::PAGED ? 1 : 2;
-  static constexpr int KS = KSTEPS / PHASES;              // k-steps held in registers at once
-  uint4 d[KS][NV];
-  uint32_t sc[KS];
-  uint4 last[2];
+  static constexpr int PER_PHASE = PER_WARP / PHASES;
+  static_assert(KSTEPS * UNITS_PER_KSTEP % WARPS == 0 && PER_WARP % PHASES == 0, "unit split");
+  uint4 d[PER_PHASE];
 };
 
-// The list entries this lane's staged rows come from, for the tile starting at j0.
-// Fetched one tile ahead so that the row loads never wait on an index load.
-__device__ __forceinline__ void index_load(int (&idx)[KSTEPS], const ListView& lv, int j0,
-                                           int warp, int lane) {
-  const int rh = warp >> 3, r = lane >> 2;
-#pragma unroll
-  for (int j = 0; j < KSTEPS; ++j) idx[j] = list_index(lv, j0 + 16 * j + 8 * rh + r);
+struct UnitPos { int j, row, ci; };   // k-step, tile row, 16-byte chunk of the row
+
+__device__ __forceinline__ int pack_pos(const UnitPos& u) { return u.row | (u.ci << 8) | (u.j << 16); }
+__device__ __forceinline__ UnitPos unpack_pos(int v) {
+  UnitPos u;
+  u.row = v & 0xff;
+  u.ci = (v >> 8) & 0xff;
+  u.j = v >> 16;
+  return u;
 }
 
-// Issue the row loads of phase `ph` of the tile whose first list entry is j0 and whose
-// list entries are already in `tidx`.
+template <int FMT, int DQK>
+__device__ __forceinline__ UnitPos unit_pos(int i, int warp, int lane) {
+  using S = Stage<FMT, DQK>;
+  const int u = warp + WARPS * i;
+  UnitPos q;
+  q.j = u / S::UNITS_PER_KSTEP;
+  const int rem = u - q.j * S::UNITS_PER_KSTEP;
+  const int g = rem / S::LINES, c = rem - g * S::LINES;
+  q.row = 16 * q.j + 4 * g + (lane >> 3);
+  q.ci = 8 * c + (lane & 7);
+  return q;
+}
+
+// Position of unit i: from the per-thread table computed once (paged layouts; saves the
+// index arithmetic on every use) or computed on the spot (flat BF16, short of registers).
+template <int FMT, int DQK>
+__device__ __forceinline__ UnitPos pos_of(const int (&upos)[Stage<FMT, DQK>::PER_WARP], int i,
+                                          int warp, int lane) {
+  if constexpr (Cfg<FMT, DQK>::PAGED) return unpack_pos(upos[i]);
+  else return unit_pos<FMT, DQK>(i, warp, lane);
+}
+
+// The list entries of this lane's units, for the tile starting at j0.  Fetched one
+// tile ahead so that the row loads never wait on an index load.
+template <int FMT, int DQK>
+__device__ __forceinline__ void index_load(int (&idx)[Stage<FMT, DQK>::PER_WARP],
+                                           const int (&upos)[Stage<FMT, DQK>::PER_WARP],
+                                           const ListView& lv, int j0, int warp, int lane) {
+#pragma unroll
+  for (int i = 0; i < Stage<FMT, DQK>::PER_WARP; ++i)
+    idx[i] = list_index(lv, j0 + pos_of<FMT, DQK>(upos, i, warp, lane).row);
+}
+
+// Row start of list entry (j, idx), or null when it gathers nothing; `scl` gets the
+// address of its scale bytes (paged layouts).
+template <int FMT>
+__device__ __forceinline__ const uint8_t* row_ptr(const AttnParams& p, const ListView& lv, int j,
+                                                  int idx, const uint8_t*& scl) {
+  const bool is_main = j < lv.len;
+  const int ntok = is_main ? p.n_tok : p.extra_n_tok;
+  scl = nullptr;
+  if (idx < 0 || idx >= ntok) return nullptr;
+  const uint8_t* kv = is_main ? p.kv : p.extra_kv;
+  const int64_t stride = is_main ? p.stride_kv : p.stride_extra_kv;
+  if constexpr (FMT == DSV4_KV_BF16) {
+    return kv + static_cast<int64_t>(idx) * stride * 2;
+  } else {
+    using T = KvTraits<FMT>;
+    const int pb = is_main ? p.page_block : p.extra_page_block;
+    const int sh = is_main ? p.page_shift : p.extra_page_shift;
+    const int page = sh >= 0 ? (idx >> sh) : (idx / pb);
+    const int rr = idx - page * pb;
+    const uint8_t* pbase = kv + static_cast<int64_t>(page) * stride;
+    scl = pbase + pb * T::ROW_BYTES + rr * T::SLOTS;
+    return pbase + rr * T::ROW_BYTES;
+  }
+}
+
+// Issue the row loads of phase `ph` of the tile whose first list entry is j0.
 template <int FMT, int DQK>
 __device__ __forceinline__ void stage_load(Stage<FMT, DQK>& st, const AttnParams& p,
-                                           const ListView& lv, const int (&tidx)[KSTEPS], int j0,
+                                           const ListView& lv,
+                                           const int (&tidx)[Stage<FMT, DQK>::PER_WARP],
+                                           const int (&upos)[Stage<FMT, DQK>::PER_WARP], int j0,
                                            int ph, int warp, int lane) {
   using S = Stage<FMT, DQK>;
-  using C = Cfg<FMT, DQK>;
-  const int blk = warp & 7, rh = warp >> 3, r = lane >> 2, q = lane & 3;
-  const bool has_main = blk < C::MAIN_BLOCKS;
-  int idx[S::KS];
 #pragma unroll
-  for (int jj = 0; jj < S::KS; ++jj) idx[jj] = tidx[ph * S::KS + jj];
-#pragma unroll
-  for (int jj = 0; jj < S::KS; ++jj) {
-    const int j = ph * S::KS + jj;
-    const bool is_main = (j0 + 16 * j + 8 * rh + r) < lv.len;
-    const int ntok = is_main ? p.n_tok : p.extra_n_tok;
-    const bool valid = idx[jj] >= 0 && idx[jj] < ntok;
-    const uint8_t* kv = is_main ? p.kv : p.extra_kv;
-    const int64_t stride = is_main ? p.stride_kv : p.stride_extra_kv;
-    const uint8_t* row = nullptr;
-    const uint8_t* scl = nullptr;
-    if (valid) {
-      if constexpr (C::PAGED) {
-        using T = KvTraits<FMT>;
-        const int pb = is_main ? p.page_block : p.extra_page_block;
-        const int sh = is_main ? p.page_shift : p.extra_page_shift;
-        const int page = sh >= 0 ? (idx[jj] >> sh) : (idx[jj] / pb);
-        const int rr = idx[jj] - page * pb;
-        const uint8_t* pbase = kv + static_cast<int64_t>(page) * stride;
-        row = pbase + rr * T::ROW_BYTES;
-        scl = pbase + pb * T::ROW_BYTES + rr * T::SLOTS;
-      } else {
-        row = kv + static_cast<int64_t>(idx[jj]) * stride * 2;
-      }
-    }
-#pragma unroll
-    for (int k = 0; k < S::NV; ++k) st.d[jj][k] = make_uint4(0, 0, 0, 0);
-    st.sc[jj] = 0x7f7f7f7fu;
-    if (valid && has_main) {
-      if constexpr (C::PAGED) {
-        st.d[jj][0] = ldg16(row + 64 * blk + 16 * q);
-        const int tile_no = blk * 64 / KvTraits<FMT>::TILE;
-        st.sc[jj] = __ldg(reinterpret_cast<const uint32_t*>(scl) + (tile_no >> 2));
-      } else {
-        st.d[jj][0] = ldg16(row + 128 * blk + 32 * q);
-        st.d[jj][1] = ldg16(row + 128 * blk + 32 * q + 16);
-      }
-    }
-    if (C::HAS_LAST && j == blk) {
-      st.last[0] = st.last[1] = make_uint4(0, 0, 0, 0);
-      if (valid) {
-        st.last[0] = ldg16(row + C::LAST_SRC_OFFSET + 32 * q);
-        st.last[1] = ldg16(row + C::LAST_SRC_OFFSET + 32 * q + 16);
-      }
-    }
+  for (int ii = 0; ii < S::PER_PHASE; ++ii) {
+    const int i = ph * S::PER_PHASE + ii;
+    const UnitPos u = pos_of<FMT, DQK>(upos, i, warp, lane);
+    const uint8_t* scl;
+    const uint8_t* row = row_ptr<FMT>(p, lv, j0 + u.row, tidx[i], scl);
+    st.d[ii] = make_uint4(0, 0, 0, 0);
+    if (row != nullptr && u.ci < S::CH) st.d[ii] = ldg16(row + 16 * u.ci);
   }
 }
 
-// Convert and store k-step j (held at register slot jj) into the swizzled K tile.
+// Rare path (scale byte 0 or > 134): two multiplies per pair; kept out of line.
+static __device__ __noinline__ void dequant16_two_mul(uint4 v, ScaleMul mul, uint32_t (&o)[8]) {
+  dequant4_fast(v.x, mul, o[0], o[1]);
+  dequant4_fast(v.y, mul, o[2], o[3]);
+  dequant4_fast(v.z, mul, o[4], o[5]);
+  dequant4_fast(v.w, mul, o[6], o[7]);
+}
+
+// Convert and store staged unit (register slot ii) into the swizzled K tile.
+// `sc_tab` is this tile's scale table: SLOTS / 4 32-bit words per row.
 template <int FMT, int DQK>
-__device__ __forceinline__ void stage_store(const Stage<FMT, DQK>& st, uint32_t sK, int j, int jj,
-                                            int warp, int lane) {
+__device__ __forceinline__ void stage_store(const Stage<FMT, DQK>& st, uint32_t sK,
+                                            const uint32_t* sc_tab, const UnitPos& u, int ii) {
+  using S = Stage<FMT, DQK>;
   using C = Cfg<FMT, DQK>;
-  const int blk = warp & 7, rh = warp >> 3, r = lane >> 2, q = lane & 3;
-  const uint32_t rbase = sK + (16 * j + 8 * rh + r) * 128;      // (row & 7) == r
-  const uint32_t c0 = ((2 * q) ^ r) << 4, c1 = ((2 * q + 1) ^ r) << 4;
-  if (blk < C::MAIN_BLOCKS) {
-    const uint32_t a = rbase + blk * KBLOCK_BYTES;
-    if constexpr (C::PAGED) {
-      const int tile_no = blk * 64 / KvTraits<FMT>::TILE;
-      const ScaleMul mul = make_scale_mul((st.sc[jj] >> (8 * (tile_no & 3))) & 0xffu);
+  const int x = u.row & 7;
+  const uint32_t rbase = sK + u.row * 128;
+  const uint4 v = st.d[ii];
+  if constexpr (C::PAGED) {
+    using T = KvTraits<FMT>;
+    if (u.ci < S::FP8_CH) {
+      const int blk = u.ci >> 2, c2 = 2 * (u.ci & 3);
+      const int sb = u.ci * 16 / T::TILE;                       // scale byte of this chunk
+      const uint32_t word = sc_tab[u.row * (T::SLOTS / 4) + (sb >> 2)];
+      const ScaleMul mul = make_scale_mul((word >> (8 * (sb & 3))) & 0xffu);
       uint32_t o[8];
-      dequant4_fast(st.d[jj][0].x, mul, o[0], o[1]);
-      dequant4_fast(st.d[jj][0].y, mul, o[2], o[3]);
-      dequant4_fast(st.d[jj][0].z, mul, o[4], o[5]);
-      dequant4_fast(st.d[jj][0].w, mul, o[6], o[7]);
-      st_shared_v4(a + c0, o[0], o[1], o[2], o[3]);
-      st_shared_v4(a + c1, o[4], o[5], o[6], o[7]);
-    } else {
-      st_shared_v4(a + c0, st.d[jj][0].x, st.d[jj][0].y, st.d[jj][0].z, st.d[jj][0].w);
-      st_shared_v4(a + c1, st.d[jj][1].x, st.d[jj][1].y, st.d[jj][1].z, st.d[jj][1].w);
+      if (mul.c2 == 0) {                       // scale bytes 1..134: one multiply per pair
+        dequant4_one_mul(v.x, mul.c1, o[0], o[1]);
+        dequant4_one_mul(v.y, mul.c1, o[2], o[3]);
+        dequant4_one_mul(v.z, mul.c1, o[4], o[5]);
+        dequant4_one_mul(v.w, mul.c1, o[6], o[7]);
+      } else {
+        dequant16_two_mul(v, mul, o);
+      }
+      const uint32_t a = rbase + blk * KBLOCK_BYTES;
+      st_shared_v4(a + ((c2 ^ x) << 4), o[0], o[1], o[2], o[3]);
+      st_shared_v4(a + (((c2 + 1) ^ x) << 4), o[4], o[5], o[6], o[7]);
+    } else if (u.ci < S::CH) {
+      const uint32_t a = rbase + (C::NB - 1) * KBLOCK_BYTES;
+      st_shared_v4(a + (((u.ci - S::FP8_CH) ^ x) << 4), v.x, v.y, v.z, v.w);
     }
-  }
-  if (C::HAS_LAST && j == blk) {
-    const uint32_t a = rbase + (C::NB - 1) * KBLOCK_BYTES;
-    st_shared_v4(a + c0, st.last[0].x, st.last[0].y, st.last[0].z, st.last[0].w);
-    st_shared_v4(a + c1, st.last[1].x, st.last[1].y, st.last[1].z, st.last[1].w);
+  } else {
+    const uint32_t a = rbase + (u.ci >> 3) * KBLOCK_BYTES;
+    st_shared_v4(a + (((u.ci & 7) ^ x) << 4), v.x, v.y, v.z, v.w);
   }
 }
 
@@ -341,9 +379,31 @@ sm100_attn_kernel(const AttnParams p) {
 
   // The first tile's gather goes in flight before anything else.
   S stage;
-  int tidx[KSTEPS];
-  index_load(tidx, lv, lv.begin, warp, lane);
-  stage_load(stage, p, lv, tidx, lv.begin, 0, warp, lane);
+  int tidx[S::PER_WARP], upos[S::PER_WARP];
+#pragma unroll
+  for (int i = 0; i < S::PER_WARP; ++i) upos[i] = pack_pos(unit_pos<FMT, DQK>(i, warp, lane));
+  index_load<FMT, DQK>(tidx, upos, lv, lv.begin, warp, lane);
+  // Softmax geometry: TMEM lanes 32*lg.. (tile rows), head columns 16*cg..16*cg+15.
+  const int lg = warp & 3, cg = warp >> 2;
+  const int row = lg * 32 + lane;
+  // The list entry of this thread's own tile row (masking; scale-table fill by tid < 128).
+  int ridx = list_index(lv, lv.begin + row);
+  stage_load(stage, p, lv, tidx, upos, lv.begin, 0, warp, lane);
+  // Scale words of tile row `tid` into the table of tile `slot` (threads 0..127).
+  auto fill_scales = [&](int slot, int j, int idx) {
+    if constexpr (C::PAGED) {
+      constexpr int SC_WORDS = KvTraits<FMT>::SLOTS / 4;
+      if (tid < TILE) {
+        const uint8_t* scl;
+        const uint8_t* r = row_ptr<FMT>(p, lv, j, j < lv.end ? idx : -1, scl);
+#pragma unroll
+        for (int k = 0; k < SC_WORDS; ++k)
+          ctrl.sc_tab[slot][tid * SC_WORDS + k] =
+              r != nullptr ? __ldg(reinterpret_cast<const uint32_t*>(scl) + k) : 0x7f7f7f7fu;
+      }
+    }
+  };
+  fill_scales(0, lv.begin + row, ridx);
 
   // ---- set-up: barriers, TMEM, Q ---------------------------------------------------
   if (tid == 0) {
@@ -422,26 +482,21 @@ sm100_attn_kernel(const AttnParams p) {
     if (ok && !mbar_wait(bar_k_full, t & 1)) { atomicExch(&g_attn_error, ERR_KFULL); ok = false; }
     tc_fence_after_sync();
     TSTAMP(t, 1);
-#pragma unroll 1
-    for (int kb = 0; kb < C::NB; ++kb) {
-      const uint32_t a = dK_lo + ((kb * KBLOCK_BYTES) >> 4), b = dQ_lo + ((kb * QBLOCK_BYTES) >> 4);
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks)
-        umma_bf16_lohi(tmem + COL_S, a + 2 * ks, dK_hi, b + 2 * ks, dQ_hi, idesc_qk, (kb | ks) != 0);
-    }
+    for (int kb = 0; kb < C::NB; ++kb)       // four 16-wide steps of one 64-column block
+      umma_bf16_x4(tmem + COL_S, 0, dK_lo + ((kb * KBLOCK_BYTES) >> 4), dK_hi, 2,
+                   dQ_lo + ((kb * QBLOCK_BYTES) >> 4), dQ_hi, 2, idesc_qk, kb != 0, 1);
     umma_commit(bar_s_full);
   };
   auto issue_pv = [&](int t, bool last, bool& ok) {
     if (ok && !mbar_wait(bar_p_full, t & 1)) { atomicExch(&g_attn_error, ERR_PFULL); ok = false; }
     tc_fence_after_sync();
     TSTAMP(t, 5);
-#pragma unroll 1
-    for (int j = 0; j < KSTEPS; ++j) {
-      const uint32_t a = dV_lo + ((j * 2048) >> 4), b = dP_lo + ((j * 2048) >> 4);
 #pragma unroll
-      for (int m = 0; m < D_V / 128; ++m)
-        umma_bf16_lohi(tmem + COL_O + m * HEADS, a + ((m * 2 * KBLOCK_BYTES) >> 4), dV_hi, b, dP_hi,
-                       idesc_pv, (t | j) != 0);
+    for (int j = 0; j < KSTEPS; ++j) {       // the four 128-row slices of O^T for one k-step
+      const uint32_t acc = (t | j) != 0;
+      umma_bf16_x4(tmem + COL_O, HEADS, dV_lo + ((j * 2048) >> 4), dV_hi, (2 * KBLOCK_BYTES) >> 4,
+                   dP_lo + ((j * 2048) >> 4), dP_hi, 0, idesc_pv, acc, acc);
       umma_commit(bar_kv_free0 + 8 * j);
     }
     if (last) umma_commit(bar_o_done);
@@ -452,18 +507,22 @@ sm100_attn_kernel(const AttnParams p) {
   // that tile has retired.  After a wait has given up (`ok` false) no further wait is
   // attempted, but every thread keeps walking the same path so that the CTA-wide
   // barriers below stay matched; the outputs are then suppressed.
-  auto refill = [&](int j0, int wait_tile, bool& ok) {
+  auto refill = [&](int j0, int wait_tile, int slot, bool& ok) {
+    int waited = -1;                       // k-steps <= waited are known to be free
 #pragma unroll
     for (int ph = 0; ph < S::PHASES; ++ph) {
-      if (ph > 0) stage_load(stage, p, lv, tidx, j0, ph, warp, lane);
+      if (ph > 0) stage_load(stage, p, lv, tidx, upos, j0, ph, warp, lane);
 #pragma unroll
-      for (int jj = 0; jj < S::KS; ++jj) {
-        const int j = ph * S::KS + jj;
-        if (wait_tile >= 0 && ok && !mbar_wait_warp(bar_kv_free0 + 8 * j, wait_tile & 1, lane)) {
-          atomicExch(&g_attn_error, ERR_KVFREE);
-          ok = false;
+      for (int ii = 0; ii < S::PER_PHASE; ++ii) {
+        const UnitPos u = pos_of<FMT, DQK>(upos, ph * S::PER_PHASE + ii, warp, lane);
+        if (wait_tile >= 0 && u.j > waited) {
+          if (ok && !mbar_wait_warp(bar_kv_free0 + 8 * u.j, wait_tile & 1, lane)) {
+            atomicExch(&g_attn_error, ERR_KVFREE);
+            ok = false;
+          }
+          waited = u.j;
         }
-        stage_store(stage, sK, j, jj, warp, lane);
+        stage_store(stage, sK, ctrl.sc_tab[slot], u, ii);
       }
     }
     fence_async_smem();
@@ -471,36 +530,37 @@ sm100_attn_kernel(const AttnParams p) {
     if (lane == 0) mbar_arrive(bar_k_full);
   };
 
-  // Softmax geometry: TMEM lanes 32*lg.. (tile rows), head columns 16*cg..16*cg+15.
-  const int lg = warp & 3, cg = warp >> 2;
-  const int row = lg * 32 + lane;
   const uint32_t tlane = static_cast<uint32_t>(lg * 32) << 16;
   const float cs = p.sm_scale * LOG2E;
   float lsum[COLS_PER_WARP];
 #pragma unroll
   for (int i = 0; i < COLS_PER_WARP; ++i) lsum[i] = 0.f;
 
-  if (tid == 0) TSTAMP(0, 6);
-  refill(lv.begin, -1, ok);
-  if (tid == 0) TSTAMP(0, 0);
-  if (n_tiles > 1) index_load(tidx, lv, lv.begin + TILE, warp, lane);
+  int ridx_next = -1;
 
-  for (int t = 0; t < n_tiles; ++t) {
+  // Iteration t = -1 only fills the first tile; iteration t >= 0 runs tile t and, behind
+  // its P.V product, fills tile t + 1.
+#pragma unroll 1
+  for (int t = -1; t < n_tiles; ++t) {
+    const bool more = t + 1 < n_tiles;
+    if (t >= 0) {
+    if (tid == 0) issue_qk(t, ok);
+    __syncwarp();
+    if (more) {
+      stage_load(stage, p, lv, tidx, upos, lv.begin + (t + 1) * TILE, 0, warp, lane);
+      fill_scales((t + 1) & 1, lv.begin + (t + 1) * TILE + row, ridx_next);   // read after the syncs below
+    }
+    if (tid == 0 && t > 0) TSTAMP(t, 6);
     // Is this thread's row masked (beyond the range, or an invalid entry under masking rules)?
     bool masked = true;
     {
       const int j = lv.begin + t * TILE + row;
       if (j < lv.end) {
-        const int idx = list_index(lv, j);
         const int ntok = (j < lv.len) ? p.n_tok : p.extra_n_tok;
-        masked = !(idx >= 0 && idx < ntok) && mask_invalid;
+        masked = !(ridx >= 0 && ridx < ntok) && mask_invalid;
       }
     }
-    if (tid == 0) issue_qk(t, ok);
-    __syncwarp();
-    const bool more = t + 1 < n_tiles;
-    if (more) stage_load(stage, p, lv, tidx, lv.begin + (t + 1) * TILE, 0, warp, lane);
-    if (tid == 0 && t > 0) TSTAMP(t, 6);
+    ridx = ridx_next;
 
     if (ok && !mbar_wait_warp(bar_s_full, t & 1, lane)) { atomicExch(&g_attn_error, ERR_SFULL); ok = false; }
     tc_fence_after_sync();
@@ -508,13 +568,15 @@ sm100_attn_kernel(const AttnParams p) {
 
     // pass 1: per-head max over the tile's rows
     {
-      float v[16];
       uint32_t ra[16];
       tmem_ld16(tmem + tlane + COL_S + cg * 16, ra);
       tmem_ld_wait();
+      float cm = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = masked ? -INFINITY : __uint_as_float(ra[i]);
-      const float cm = warp_col_reduce16<true>(v, lane);
+      for (int i = 0; i < 16; ++i) {
+        const float m = warp_max_f32(masked ? -INFINITY : __uint_as_float(ra[i]));
+        cm = (lane == i) ? m : cm;
+      }
       if (lane < 16) ctrl.wred[lg][cg * 16 + lane] = cm;
     }
     __syncthreads();
@@ -597,10 +659,15 @@ sm100_attn_kernel(const AttnParams p) {
     }
     __syncwarp();
 
-    // refill the tile behind the P.V product
+    }  // t >= 0
+
+    // fill tile t + 1 (behind the P.V product of tile t, if there is one)
     if (more) {
-      refill(lv.begin + (t + 1) * TILE, t, ok);
-      if (t + 2 < n_tiles) index_load(tidx, lv, lv.begin + (t + 2) * TILE, warp, lane);
+      refill(lv.begin + (t + 1) * TILE, t, (t + 1) & 1, ok);
+      if (t + 2 < n_tiles) {
+        index_load<FMT, DQK>(tidx, upos, lv, lv.begin + (t + 2) * TILE, warp, lane);
+        ridx_next = list_index(lv, lv.begin + (t + 2) * TILE + row);
+      }
       if (tid == 0) TSTAMP(t + 1, 0);
       if (tid == THREADS - 32) TSTAMP(t + 1, 7);
     }
