@@ -49,7 +49,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uin
 // with a time hint was observed to sleep for the whole hint).  Gives up after
 // `limit` probes (roughly a tenth of a second) and returns false, so that a
 // protocol error ends the kernel with a status code instead of a hang.
-static __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = (1u << 21)) {
+// Always inlined: a call would make the compiler wait for every load still in flight
+// (the staged gather) before entering it.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
+                                          uint32_t limit = (1u << 21)) {
   for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_test(bar, parity)) return true;
     if (i > 8) __nanosleep(20);
@@ -60,7 +63,7 @@ static __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uin
 // of waiters on shared memory at one per warp.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int lane) {
   uint32_t ok = 1;
-  if (lane == 0) ok = (mbar_test(bar, parity) || mbar_wait(bar, parity)) ? 1u : 0u;
+  if (lane == 0) ok = mbar_wait(bar, parity) ? 1u : 0u;
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 

@@ -58,6 +58,9 @@ constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_S = 0, COL_O = 64;
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 constexpr float RESCALE_THRESHOLD = 8.0f;             // log2 units
+// The thread that issues the MMAs: lane 0 of the last warp, whose share of the K tile is
+// released last by the P.V product, so that the (blocking) issue delays no refill.
+constexpr int ISSUE_TID = THREADS - 32;
 
 enum ErrCode { ERR_KFULL = 1, ERR_PFULL = 2, ERR_SFULL = 3, ERR_KVFREE = 4, ERR_ODONE = 5 };
 
@@ -69,6 +72,9 @@ template <int FMT, int DQK> struct Cfg {
   static constexpr int K_BYTES = NB * KBLOCK_BYTES;
   static constexpr int Q_BYTES = NB * QBLOCK_BYTES;
   static constexpr int P_BYTES = P_ALIAS ? 0 : TILE * 128;
+  // words per tile row in the multiplier table: V32 has 4 scale bytes, MODEL1 7 (padded to 8)
+  static constexpr int MUL_PER_ROW = !PAGED ? 0 : (DQK == 576 ? 4 : 8);
+  static constexpr int MUL_TAB_BYTES = 2 * TILE * MUL_PER_ROW * 4;      // double-buffered
 };
 
 struct Ctrl {
@@ -82,13 +88,12 @@ struct Ctrl {
   float muse[HEADS];                   // mref with -inf replaced by 0 (exponent offset)
   float mtrue[HEADS];                  // true running max, log2-scaled units
   float alpha[HEADS];                  // rescale factor / final output factor
-  uint32_t sc_tab[2][TILE * 2];        // per-tile scale words of the tile rows (double-buffered)
 };
 
 template <int FMT, int DQK>
 constexpr size_t smem_bytes() {
   using C = Cfg<FMT, DQK>;
-  return 1024 + C::K_BYTES + C::Q_BYTES + C::P_BYTES + sizeof(Ctrl);
+  return 1024 + C::K_BYTES + C::Q_BYTES + C::P_BYTES + sizeof(Ctrl) + C::MUL_TAB_BYTES;
 }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -99,8 +104,10 @@ __device__ __forceinline__ float ex2(float x) {
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
                                              uint32_t d) {
+  // volatile keeps it ordered against the barrier waits and fences (also volatile); no
+  // memory clobber, so that independent conversions can be scheduled around it
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c),
-               "r"(d) : "memory");
+               "r"(d));
 }
 
 __device__ __forceinline__ uint4 ldg16(const uint8_t* p) {
@@ -130,6 +137,39 @@ __device__ __forceinline__ float warp_col_reduce16(float (&v)[16], int lane) {
   return v[0];
 }
 
+__device__ __forceinline__ uint32_t bf16x2_max(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// Column-wise maximum, over the 32 lanes of a warp, of 16 columns held one row per lane.
+// Values are rounded to BF16 first (packed pairs halve the shuffles); the result only
+// serves as the softmax reference point, which needs to be the same for every thread,
+// not exact.  Lane l returns the maximum of column l & 15.
+__device__ __forceinline__ float warp_col_max16_bf16(const float (&v)[16], int lane) {
+  uint32_t pk[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    pk[i] = *reinterpret_cast<uint32_t*>(&t);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) pk[i] = bf16x2_max(pk[i], __shfl_xor_sync(0xffffffffu, pk[i], 16));
+#pragma unroll
+  for (int w = 4; w >= 1; w >>= 1) {            // lanes 8, 4, 2 apart: halve the register set
+    const bool up = (lane & (2 * w)) != 0;
+#pragma unroll
+    for (int i = 0; i < w; ++i) {
+      const uint32_t mine = up ? pk[w + i] : pk[i];
+      const uint32_t other = up ? pk[i] : pk[w + i];
+      pk[i] = bf16x2_max(mine, __shfl_xor_sync(0xffffffffu, other, 2 * w));
+    }
+  }
+  const uint32_t r = bf16x2_max(pk[0], __shfl_xor_sync(0xffffffffu, pk[0], 1));
+  return __uint_as_float((lane & 1) ? (r & 0xffff0000u) : (r << 16));
+}
+
 // Debug timeline: SM cycle counter of CTA (0,0,0) into p.prof[slot] when a buffer is set.
 __device__ __forceinline__ void stamp(const AttnParams& p, int slot) {
   if (p.prof != nullptr && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) p.prof[slot] = clock64();
@@ -143,179 +183,175 @@ struct ListView {
 };
 
 // List entry j without branching: entries past the end of the range read as -1.
+// EXTRA says whether a second (extra) list may follow the main one.
+template <bool EXTRA>
 __device__ __forceinline__ int list_index(const ListView& lv, int j) {
   const bool in_range = j < lv.end;
-  const bool is_main = j < lv.len;
-  const int32_t* src = is_main ? lv.main_idx + j : lv.extra_idx + (j - lv.len);
+  const int32_t* src = lv.main_idx + j;
+  if constexpr (EXTRA) {
+    if (j >= lv.len) src = lv.extra_idx + (j - lv.len);
+  }
   return in_range ? __ldg(src) : -1;
 }
 
 // ---------------------------------------------------------------------------
 // Register staging of one tile.  A tile is 8 "k-steps" of 16 rows (the rows one
-// P.V MMA step contracts over).  The unit of gather work is one 128-byte line of
-// four rows: 8 lanes x 16 bytes cover the line of a row, so a warp-wide load
-// touches four cache lines (a gather's cost in the L1 is per line touched).
-// Units are numbered k-step-major and dealt round-robin to the 16 warps, so that
-// when P.V retires k-step j all warps refill those 16 rows together and the
-// refill of the tile trails the product by one k-step.
+// P.V MMA step contracts over).  Warp w owns, in the two k-steps j = (w >> 2) and
+// j = 4 + (w >> 2), the four rows 4 * (w & 3) .. +4: lane l holds, for each
+// 128-byte line c of a row, the 16-byte chunk 8 c + (l & 7) of row (l >> 3).
+// So a warp-wide load touches four cache lines, the line number is a
+// compile-time constant of every load/convert/store (addresses reduce to a
+// per-thread base plus an immediate), and a warp needs two list entries and two
+// waits per tile.  When P.V retires k-step j the four warps owning it refill it;
+// the owners of different k-steps sit on different schedulers.
 //   paged layouts: a row is CH 16-byte chunks: FP8 chunks (16 values -> two BF16
 //                  chunks of block chunk/4) then 8 RoPE chunks (copied to the last block);
 //   flat BF16:     a row is d_qk/8 chunks copied as they are; rows are twice as wide,
-//                  so they are staged half a tile at a time.
-// Scale bytes come from a per-tile table in shared memory (one load per row).
+//                  so the two k-steps are staged one after the other.
+// Scale factors come from a per-tile table in shared memory (one load per row).
 // ---------------------------------------------------------------------------
 template <int FMT, int DQK> struct Stage {
   using C = Cfg<FMT, DQK>;
   static constexpr int CH = C::PAGED ? C::NOPE_SEGS * 4 + 8 : DQK / 8;   // 16-byte chunks per row
   static constexpr int FP8_CH = C::PAGED ? C::NOPE_SEGS * 4 : 0;
   static constexpr int LINES = (CH + 7) / 8;
-  static constexpr int UNITS_PER_KSTEP = 4 * LINES;
-  static constexpr int PER_WARP = KSTEPS * UNITS_PER_KSTEP / WARPS;      // 10, 16 or 18
   static constexpr int PHASES = C::PAGED ? 1 : 2;
-  static constexpr int PER_PHASE = PER_WARP / PHASES;
-  static_assert(KSTEPS * UNITS_PER_KSTEP % WARPS == 0 && PER_WARP % PHASES == 0, "unit split");
-  uint4 d[PER_PHASE];
+  static constexpr int HALVES = 2 / PHASES;                // k-steps held in registers at once
+  uint4 d[HALVES][LINES];
 };
 
-struct UnitPos { int j, row, ci; };   // k-step, tile row, 16-byte chunk of the row
+// Per-thread constants of the staging geometry.
+struct Geo {
+  int jsub;     // k-steps handled: jsub and 4 + jsub
+  int rloc;     // row within a k-step: 4 * (w & 3) + (l >> 3)
+  int piece;    // 16-byte chunk within a line: l & 7
+  __device__ __forceinline__ int row(int jhalf) const { return 16 * (4 * jhalf + jsub) + rloc; }
+};
 
-__device__ __forceinline__ int pack_pos(const UnitPos& u) { return u.row | (u.ci << 8) | (u.j << 16); }
-__device__ __forceinline__ UnitPos unpack_pos(int v) {
-  UnitPos u;
-  u.row = v & 0xff;
-  u.ci = (v >> 8) & 0xff;
-  u.j = v >> 16;
-  return u;
+// Cache geometry of list entry j (main or extra cache).
+struct CacheSel {
+  const uint8_t* kv;
+  int64_t stride;
+  int ntok, pb, sh;
+};
+template <bool EXTRA>
+__device__ __forceinline__ CacheSel cache_of(const AttnParams& p, const ListView& lv, int j) {
+  CacheSel c{p.kv, p.stride_kv, p.n_tok, p.page_block, p.page_shift};
+  if constexpr (EXTRA) {
+    if (j >= lv.len)
+      c = CacheSel{p.extra_kv, p.stride_extra_kv, p.extra_n_tok, p.extra_page_block, p.extra_page_shift};
+  }
+  return c;
 }
 
-template <int FMT, int DQK>
-__device__ __forceinline__ UnitPos unit_pos(int i, int warp, int lane) {
-  using S = Stage<FMT, DQK>;
-  const int u = warp + WARPS * i;
-  UnitPos q;
-  q.j = u / S::UNITS_PER_KSTEP;
-  const int rem = u - q.j * S::UNITS_PER_KSTEP;
-  const int g = rem / S::LINES, c = rem - g * S::LINES;
-  q.row = 16 * q.j + 4 * g + (lane >> 3);
-  q.ci = 8 * c + (lane & 7);
-  return q;
-}
-
-// Position of unit i: from the per-thread table computed once (paged layouts; saves the
-// index arithmetic on every use) or computed on the spot (flat BF16, short of registers).
-template <int FMT, int DQK>
-__device__ __forceinline__ UnitPos pos_of(const int (&upos)[Stage<FMT, DQK>::PER_WARP], int i,
-                                          int warp, int lane) {
-  if constexpr (Cfg<FMT, DQK>::PAGED) return unpack_pos(upos[i]);
-  else return unit_pos<FMT, DQK>(i, warp, lane);
-}
-
-// The list entries of this lane's units, for the tile starting at j0.  Fetched one
-// tile ahead so that the row loads never wait on an index load.
-template <int FMT, int DQK>
-__device__ __forceinline__ void index_load(int (&idx)[Stage<FMT, DQK>::PER_WARP],
-                                           const int (&upos)[Stage<FMT, DQK>::PER_WARP],
-                                           const ListView& lv, int j0, int warp, int lane) {
-#pragma unroll
-  for (int i = 0; i < Stage<FMT, DQK>::PER_WARP; ++i)
-    idx[i] = list_index(lv, j0 + pos_of<FMT, DQK>(upos, i, warp, lane).row);
-}
-
-// Row start of list entry (j, idx), or null when it gathers nothing; `scl` gets the
-// address of its scale bytes (paged layouts).
+// Row start of token idx, or null when idx names no row (negative or out of range);
+// `scl` gets the address of its scale bytes (paged layouts).
 template <int FMT>
-__device__ __forceinline__ const uint8_t* row_ptr(const AttnParams& p, const ListView& lv, int j,
-                                                  int idx, const uint8_t*& scl) {
-  const bool is_main = j < lv.len;
-  const int ntok = is_main ? p.n_tok : p.extra_n_tok;
+__device__ __forceinline__ const uint8_t* row_ptr(const CacheSel& c, int idx, const uint8_t*& scl) {
   scl = nullptr;
-  if (idx < 0 || idx >= ntok) return nullptr;
-  const uint8_t* kv = is_main ? p.kv : p.extra_kv;
-  const int64_t stride = is_main ? p.stride_kv : p.stride_extra_kv;
+  if (static_cast<unsigned>(idx) >= static_cast<unsigned>(c.ntok)) return nullptr;
   if constexpr (FMT == DSV4_KV_BF16) {
-    return kv + static_cast<int64_t>(idx) * stride * 2;
+    return c.kv + static_cast<int64_t>(idx) * c.stride * 2;
   } else {
     using T = KvTraits<FMT>;
-    const int pb = is_main ? p.page_block : p.extra_page_block;
-    const int sh = is_main ? p.page_shift : p.extra_page_shift;
-    const int page = sh >= 0 ? (idx >> sh) : (idx / pb);
-    const int rr = idx - page * pb;
-    const uint8_t* pbase = kv + static_cast<int64_t>(page) * stride;
-    scl = pbase + pb * T::ROW_BYTES + rr * T::SLOTS;
+    const int page = c.sh >= 0 ? (idx >> c.sh) : (idx / c.pb);
+    const int rr = idx - page * c.pb;
+    const uint8_t* pbase = c.kv + static_cast<int64_t>(page) * c.stride;
+    scl = pbase + c.pb * T::ROW_BYTES + rr * T::SLOTS;
     return pbase + rr * T::ROW_BYTES;
   }
 }
 
-// Issue the row loads of phase `ph` of the tile whose first list entry is j0.
-template <int FMT, int DQK>
-__device__ __forceinline__ void stage_load(Stage<FMT, DQK>& st, const AttnParams& p,
-                                           const ListView& lv,
-                                           const int (&tidx)[Stage<FMT, DQK>::PER_WARP],
-                                           const int (&upos)[Stage<FMT, DQK>::PER_WARP], int j0,
-                                           int ph, int warp, int lane) {
+// Issue the loads of this lane's row of k-step 4 * jhalf + jsub (list entry j, token
+// idx) into one register set.
+template <int FMT, int DQK, bool EXTRA>
+__device__ __forceinline__ void load_half(uint4 (&d)[Stage<FMT, DQK>::LINES], const AttnParams& p,
+                                          const ListView& lv, int j, int idx, int piece) {
   using S = Stage<FMT, DQK>;
+  const uint8_t* scl;
+  const uint8_t* row = row_ptr<FMT>(cache_of<EXTRA>(p, lv, j), idx, scl);
+  const uint8_t* src = row + 16 * piece;
 #pragma unroll
-  for (int ii = 0; ii < S::PER_PHASE; ++ii) {
-    const int i = ph * S::PER_PHASE + ii;
-    const UnitPos u = pos_of<FMT, DQK>(upos, i, warp, lane);
-    const uint8_t* scl;
-    const uint8_t* row = row_ptr<FMT>(p, lv, j0 + u.row, tidx[i], scl);
-    st.d[ii] = make_uint4(0, 0, 0, 0);
-    if (row != nullptr && u.ci < S::CH) st.d[ii] = ldg16(row + 16 * u.ci);
+  for (int c = 0; c < S::LINES; ++c) {
+    d[c] = make_uint4(0, 0, 0, 0);
+    const bool in_row = (8 * c + 7 < S::CH) || (8 * c + piece < S::CH);
+    if (row != nullptr && in_row) d[c] = ldg16(src + 128 * c);
   }
 }
 
-// Rare path (scale byte 0 or > 134): two multiplies per pair; kept out of line.
-static __device__ __noinline__ void dequant16_two_mul(uint4 v, ScaleMul mul, uint32_t (&o)[8]) {
-  dequant4_fast(v.x, mul, o[0], o[1]);
-  dequant4_fast(v.y, mul, o[2], o[3]);
-  dequant4_fast(v.z, mul, o[4], o[5]);
-  dequant4_fast(v.w, mul, o[6], o[7]);
+// Raw scale byte `sb` of token idx; used only where the multiplier table holds 0.
+template <int FMT>
+static __device__ __noinline__ uint32_t rare_scale_byte(const uint8_t* kv, int64_t stride, int ntok,
+                                                        int pb, int sh, int idx, int sb) {
+  const CacheSel c{kv, stride, ntok, pb, sh};
+  const uint8_t* scl;
+  const uint8_t* r = row_ptr<FMT>(c, idx, scl);
+  return r != nullptr ? scl[sb] : 0x7fu;
 }
 
-// Convert and store staged unit (register slot ii) into the swizzled K tile.
-// `sc_tab` is this tile's scale table: SLOTS / 4 32-bit words per row.
-template <int FMT, int DQK>
-__device__ __forceinline__ void stage_store(const Stage<FMT, DQK>& st, uint32_t sK,
-                                            const uint32_t* sc_tab, const UnitPos& u, int ii) {
+// Convert and store line C of the staged row `v` (tile row `row`).  `mul_row` points at
+// the row's entries of the multiplier table: one packed-BF16 factor 2^(s-7) per scale
+// byte s, or 0 where s needs the two-factor path (s = 0 or s > 134).
+template <int FMT, int DQK, int LINE, class RawScale>
+__device__ __forceinline__ void store_line(const uint4& v, uint32_t sK, int row, int piece,
+                                           const uint32_t (&mul_row)[Cfg<FMT, DQK>::MUL_PER_ROW + 1],
+                                           RawScale raw_scale) {
   using S = Stage<FMT, DQK>;
   using C = Cfg<FMT, DQK>;
-  const int x = u.row & 7;
-  const uint32_t rbase = sK + u.row * 128;
-  const uint4 v = st.d[ii];
+  const int x = row & 7;
+  const uint32_t rbase = sK + row * 128;
+  const int ci = 8 * LINE + piece;
   if constexpr (C::PAGED) {
     using T = KvTraits<FMT>;
-    if (u.ci < S::FP8_CH) {
-      const int blk = u.ci >> 2, c2 = 2 * (u.ci & 3);
-      const int sb = u.ci * 16 / T::TILE;                       // scale byte of this chunk
-      const uint32_t word = sc_tab[u.row * (T::SLOTS / 4) + (sb >> 2)];
-      const ScaleMul mul = make_scale_mul((word >> (8 * (sb & 3))) & 0xffu);
-      uint32_t o[8];
-      if (mul.c2 == 0) {                       // scale bytes 1..134: one multiply per pair
-        dequant4_one_mul(v.x, mul.c1, o[0], o[1]);
-        dequant4_one_mul(v.y, mul.c1, o[2], o[3]);
-        dequant4_one_mul(v.z, mul.c1, o[4], o[5]);
-        dequant4_one_mul(v.w, mul.c1, o[6], o[7]);
-      } else {
-        dequant16_two_mul(v, mul, o);
+    constexpr bool ALL_FP8 = 8 * LINE + 7 < S::FP8_CH, NO_FP8 = 8 * LINE >= S::FP8_CH;
+    if (ALL_FP8 || (!NO_FP8 && ci < S::FP8_CH)) {
+      const int sb = ci * 16 / T::TILE;                         // scale byte of this chunk
+      uint32_t c1;
+      if constexpr (T::TILE == 128) c1 = mul_row[LINE];         // 8 chunks per scale tile
+      else c1 = (piece & 4) ? mul_row[2 * LINE + 1] : mul_row[2 * LINE];
+      uint32_t c2 = 0;
+      if (c1 == 0) {                                            // rare
+        const ScaleMul m = make_scale_mul(raw_scale(sb));
+        c1 = m.c1;
+        c2 = m.c2;
       }
-      const uint32_t a = rbase + blk * KBLOCK_BYTES;
-      st_shared_v4(a + ((c2 ^ x) << 4), o[0], o[1], o[2], o[3]);
-      st_shared_v4(a + (((c2 + 1) ^ x) << 4), o[4], o[5], o[6], o[7]);
-    } else if (u.ci < S::CH) {
+      uint32_t o[8];
+      dequant4_one_mul(v.x, c1, o[0], o[1]);
+      dequant4_one_mul(v.y, c1, o[2], o[3]);
+      dequant4_one_mul(v.z, c1, o[4], o[5]);
+      dequant4_one_mul(v.w, c1, o[6], o[7]);
+      if (c2 != 0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = bf16x2_mul(o[k], c2);
+      }
+      const uint32_t a = rbase + (ci >> 2) * KBLOCK_BYTES + (((2 * (ci & 3)) ^ x) << 4);
+      st_shared_v4(a, o[0], o[1], o[2], o[3]);
+      st_shared_v4(a ^ 16, o[4], o[5], o[6], o[7]);             // the neighbouring chunk
+    } else if (ci < S::CH) {
       const uint32_t a = rbase + (C::NB - 1) * KBLOCK_BYTES;
-      st_shared_v4(a + (((u.ci - S::FP8_CH) ^ x) << 4), v.x, v.y, v.z, v.w);
+      st_shared_v4(a + (((ci - S::FP8_CH) ^ x) << 4), v.x, v.y, v.z, v.w);
     }
   } else {
-    const uint32_t a = rbase + (u.ci >> 3) * KBLOCK_BYTES;
-    st_shared_v4(a + (((u.ci & 7) ^ x) << 4), v.x, v.y, v.z, v.w);
+    const uint32_t a = rbase + LINE * KBLOCK_BYTES;             // line == 64-column block
+    st_shared_v4(a + ((piece ^ x) << 4), v.x, v.y, v.z, v.w);
+  }
+}
+
+template <int FMT, int DQK, int LINE, class RawScale>
+__device__ __forceinline__ void store_lines(const uint4 (&d)[Stage<FMT, DQK>::LINES], uint32_t sK,
+                                            int row, int piece,
+                                            const uint32_t (&mul_row)[Cfg<FMT, DQK>::MUL_PER_ROW + 1],
+                                            RawScale raw_scale) {
+  if constexpr (LINE < Stage<FMT, DQK>::LINES) {
+    store_line<FMT, DQK, LINE>(d[LINE], sK, row, piece, mul_row, raw_scale);
+    store_lines<FMT, DQK, LINE + 1>(d, sK, row, piece, mul_row, raw_scale);
   }
 }
 
 // ---------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------
-template <int FMT, int DQK>
+template <int FMT, int DQK, bool EXTRA>
 __global__ void __launch_bounds__(THREADS, 1)
 sm100_attn_kernel(const AttnParams p) {
   using C = Cfg<FMT, DQK>;
@@ -327,6 +363,7 @@ sm100_attn_kernel(const AttnParams p) {
   const uint32_t sK = base, sQ = base + C::K_BYTES;
   const uint32_t sP = C::P_ALIAS ? sK + (C::NB - 1) * KBLOCK_BYTES : sQ + C::Q_BYTES;
   Ctrl& ctrl = *reinterpret_cast<Ctrl*>(sm + C::K_BYTES + C::Q_BYTES + C::P_BYTES);
+  uint32_t* mul_tab = reinterpret_cast<uint32_t*>(sm + C::K_BYTES + C::Q_BYTES + C::P_BYTES + sizeof(Ctrl));
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) stamp(p, 0);
@@ -343,7 +380,7 @@ sm100_attn_kernel(const AttnParams p) {
   request_lengths(p, req, lv.len, xlen);
   split_range(lv.len + xlen, p.n_splits, split, lv.begin, lv.end);
   lv.main_idx = idx_row(p.indices, p.stride_idx_b, p.stride_idx_s, req, p.s_q);
-  lv.extra_idx = p.extra_kv ? idx_row(p.extra_indices, p.stride_xidx_b, p.stride_xidx_s, req, p.s_q)
+  lv.extra_idx = (EXTRA && p.extra_kv) ? idx_row(p.extra_indices, p.stride_xidx_b, p.stride_xidx_s, req, p.s_q)
                             : nullptr;
   const int n_tiles = (lv.end - lv.begin + TILE - 1) / TILE;
 
@@ -379,27 +416,46 @@ sm100_attn_kernel(const AttnParams p) {
 
   // The first tile's gather goes in flight before anything else.
   S stage;
-  int tidx[S::PER_WARP], upos[S::PER_WARP];
-#pragma unroll
-  for (int i = 0; i < S::PER_WARP; ++i) upos[i] = pack_pos(unit_pos<FMT, DQK>(i, warp, lane));
-  index_load<FMT, DQK>(tidx, upos, lv, lv.begin, warp, lane);
+  const Geo geo{warp >> 2, 4 * (warp & 3) + (lane >> 3), lane & 7};
+  int tidx[2];       // list entries of this lane's staged rows (k-steps jsub and 4 + jsub)
+  tidx[0] = list_index<EXTRA>(lv, lv.begin + geo.row(0));
+  tidx[1] = list_index<EXTRA>(lv, lv.begin + geo.row(1));
   // Softmax geometry: TMEM lanes 32*lg.. (tile rows), head columns 16*cg..16*cg+15.
   const int lg = warp & 3, cg = warp >> 2;
   const int row = lg * 32 + lane;
   // The list entry of this thread's own tile row (masking; scale-table fill by tid < 128).
-  int ridx = list_index(lv, lv.begin + row);
-  stage_load(stage, p, lv, tidx, upos, lv.begin, 0, warp, lane);
-  // Scale words of tile row `tid` into the table of tile `slot` (threads 0..127).
+  int ridx = list_index<EXTRA>(lv, lv.begin + row);
+#pragma unroll
+  for (int hh = 0; hh < S::HALVES; ++hh)
+    load_half<FMT, DQK, EXTRA>(stage.d[hh], p, lv, lv.begin + geo.row(hh), tidx[hh], geo.piece);
+  // List entries are fetched ahead so that no address ever waits on them: tidx / ridx
+  // belong to the tile staged in registers, tidx_next / ridx_n1 to the one after,
+  // ridx_n2 to the one after that.
+  int tidx_next[2] = {-1, -1}, ridx_n1 = -1, ridx_n2 = -1;
+  if (n_tiles > 1) {
+    tidx_next[0] = list_index<EXTRA>(lv, lv.begin + TILE + geo.row(0));
+    tidx_next[1] = list_index<EXTRA>(lv, lv.begin + TILE + geo.row(1));
+    ridx_n1 = ridx_n2 = list_index<EXTRA>(lv, lv.begin + TILE + row);
+  }
+  // Multipliers of tile row `tid` into the table of tile `slot` (threads 0..127): one
+  // load of the row's scale bytes, then a packed factor per byte (0 marks the rare bytes).
   auto fill_scales = [&](int slot, int j, int idx) {
     if constexpr (C::PAGED) {
-      constexpr int SC_WORDS = KvTraits<FMT>::SLOTS / 4;
+      using T = KvTraits<FMT>;
       if (tid < TILE) {
         const uint8_t* scl;
-        const uint8_t* r = row_ptr<FMT>(p, lv, j, j < lv.end ? idx : -1, scl);
+        const uint8_t* r = row_ptr<FMT>(cache_of<EXTRA>(p, lv, j), j < lv.end ? idx : -1, scl);
+        uint32_t w[T::SLOTS / 4];
 #pragma unroll
-        for (int k = 0; k < SC_WORDS; ++k)
-          ctrl.sc_tab[slot][tid * SC_WORDS + k] =
-              r != nullptr ? __ldg(reinterpret_cast<const uint32_t*>(scl) + k) : 0x7f7f7f7fu;
+        for (int k = 0; k < T::SLOTS / 4; ++k)
+          w[k] = r != nullptr ? __ldg(reinterpret_cast<const uint32_t*>(scl) + k) : 0x7f7f7f7fu;
+        uint32_t* dst = mul_tab + (slot * TILE + tid) * C::MUL_PER_ROW;
+#pragma unroll
+        for (int k = 0; k < T::N_SCALE; ++k) {
+          const uint32_t sbyte = (w[k >> 2] >> (8 * (k & 3))) & 0xffu;
+          const uint32_t c = (sbyte + 120u) << 7;
+          dst[k] = (sbyte >= 1 && sbyte <= 134) ? (c | (c << 16)) : 0u;
+        }
       }
     }
   };
@@ -428,10 +484,10 @@ sm100_attn_kernel(const AttnParams p) {
   }
   {
     // Q[head][d] -> blocks [d/64][head][64], 128-byte swizzle; absent heads are zero.
-    // Loads are issued three at a time so their latencies overlap.
+    // All of a thread's loads are issued before its first store so their latencies overlap.
     const __nv_bfloat16* qrow0 = p.q + bi * p.stride_q_b + si * p.stride_q_s + head0 * p.stride_q_h;
     constexpr int Q_CHUNKS = HEADS * C::NB * 8;
-    constexpr int Q_BATCH = 3;
+    constexpr int Q_BATCH = (HEADS * C::NB * 8 + THREADS - 1) / THREADS;   // all in flight at once
     constexpr int Q_ITERS = (Q_CHUNKS + THREADS * Q_BATCH - 1) / (THREADS * Q_BATCH);
 #pragma unroll 1
     for (int ob = 0; ob < Q_ITERS; ++ob) {
@@ -486,6 +542,7 @@ sm100_attn_kernel(const AttnParams p) {
     for (int kb = 0; kb < C::NB; ++kb)       // four 16-wide steps of one 64-column block
       umma_bf16_x4(tmem + COL_S, 0, dK_lo + ((kb * KBLOCK_BYTES) >> 4), dK_hi, 2,
                    dQ_lo + ((kb * QBLOCK_BYTES) >> 4), dQ_hi, 2, idesc_qk, kb != 0, 1);
+    if (t == 3) stamp(p, 130 + C::NB);
     umma_commit(bar_s_full);
   };
   auto issue_pv = [&](int t, bool last, bool& ok) {
@@ -498,6 +555,7 @@ sm100_attn_kernel(const AttnParams p) {
       umma_bf16_x4(tmem + COL_O, HEADS, dV_lo + ((j * 2048) >> 4), dV_hi, (2 * KBLOCK_BYTES) >> 4,
                    dP_lo + ((j * 2048) >> 4), dP_hi, 0, idesc_pv, acc, acc);
       umma_commit(bar_kv_free0 + 8 * j);
+      if (t == 3) stamp(p, 140 + j);
     }
     if (last) umma_commit(bar_o_done);
   };
@@ -507,27 +565,57 @@ sm100_attn_kernel(const AttnParams p) {
   // that tile has retired.  After a wait has given up (`ok` false) no further wait is
   // attempted, but every thread keeps walking the same path so that the CTA-wide
   // barriers below stay matched; the outputs are then suppressed.
-  auto refill = [&](int j0, int wait_tile, int slot, bool& ok) {
-    int waited = -1;                       // k-steps <= waited are known to be free
+  // As soon as a register set has been stored it is reloaded with the same rows of the
+  // next tile (list entries tidx_next; `has_next` false on the last tile), so the gather
+  // is spread over the whole P.V phase instead of hitting memory in one burst.
+  auto refill = [&](int j0, int wait_tile, int slot, bool has_next, bool& ok) {
 #pragma unroll
-    for (int ph = 0; ph < S::PHASES; ++ph) {
-      if (ph > 0) stage_load(stage, p, lv, tidx, upos, j0, ph, warp, lane);
+    for (int jhalf = 0; jhalf < 2; ++jhalf) {
+      const int hh = S::HALVES == 2 ? jhalf : 0;
+      const int j = 4 * jhalf + geo.jsub, trow = geo.row(jhalf);
+      if (wait_tile >= 0 && ok && !mbar_wait_warp(bar_kv_free0 + 8 * j, wait_tile & 1, lane)) {
+        atomicExch(&g_attn_error, ERR_KVFREE);
+        ok = false;
+      }
+      uint32_t mrow[C::MUL_PER_ROW + 1];          // the row's multipliers, one vector load each 4
+      if constexpr (C::PAGED) {
+        const uint4* src = reinterpret_cast<const uint4*>(mul_tab + (slot * TILE + trow) * C::MUL_PER_ROW);
 #pragma unroll
-      for (int ii = 0; ii < S::PER_PHASE; ++ii) {
-        const UnitPos u = pos_of<FMT, DQK>(upos, ph * S::PER_PHASE + ii, warp, lane);
-        if (wait_tile >= 0 && u.j > waited) {
-          if (ok && !mbar_wait_warp(bar_kv_free0 + 8 * u.j, wait_tile & 1, lane)) {
-            atomicExch(&g_attn_error, ERR_KVFREE);
-            ok = false;
-          }
-          waited = u.j;
+        for (int k = 0; k < C::MUL_PER_ROW / 4; ++k) {
+          const uint4 m4 = src[k];
+          mrow[4 * k] = m4.x; mrow[4 * k + 1] = m4.y; mrow[4 * k + 2] = m4.z; mrow[4 * k + 3] = m4.w;
         }
-        stage_store(stage, sK, ctrl.sc_tab[slot], u, ii);
+      }
+      mrow[C::MUL_PER_ROW] = 0;
+      store_lines<FMT, DQK, 0>(stage.d[hh], sK, trow, geo.piece, mrow,
+                               [&](int sb) -> uint32_t {
+        const CacheSel c = cache_of<EXTRA>(p, lv, j0 + trow);
+        return rare_scale_byte<C::PAGED ? FMT : DSV4_KV_V32>(c.kv, c.stride, c.ntok, c.pb, c.sh,
+                                                             tidx[jhalf], sb);
+      });
+      if (jhalf == 1) {                    // tile complete: publish before reloading
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_k_full);
+      }
+      if constexpr (S::HALVES == 2) {      // both k-steps staged: reload this one for the next tile
+        // The MMA-issuing warp starts its refill late (issuing blocks until the product is
+        // nearly done); it stores both k-steps first so as not to hold up k_full, and
+        // reloads afterwards.
+        const bool defer = warp == ISSUE_TID / 32;
+        if (has_next && !defer)
+          load_half<FMT, DQK, EXTRA>(stage.d[hh], p, lv, j0 + TILE + trow, tidx_next[jhalf], geo.piece);
+        if (has_next && defer && jhalf == 1) {
+          load_half<FMT, DQK, EXTRA>(stage.d[0], p, lv, j0 + TILE + geo.row(0), tidx_next[0], geo.piece);
+          load_half<FMT, DQK, EXTRA>(stage.d[1], p, lv, j0 + TILE + geo.row(1), tidx_next[1], geo.piece);
+        }
+      } else {                             // one register set: second k-step now, then the next tile
+        if (jhalf == 0)
+          load_half<FMT, DQK, EXTRA>(stage.d[0], p, lv, j0 + geo.row(1), tidx[1], geo.piece);
+        else if (has_next)
+          load_half<FMT, DQK, EXTRA>(stage.d[0], p, lv, j0 + TILE + geo.row(0), tidx_next[0], geo.piece);
       }
     }
-    fence_async_smem();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar_k_full);
   };
 
   const uint32_t tlane = static_cast<uint32_t>(lg * 32) << 16;
@@ -536,7 +624,6 @@ sm100_attn_kernel(const AttnParams p) {
 #pragma unroll
   for (int i = 0; i < COLS_PER_WARP; ++i) lsum[i] = 0.f;
 
-  int ridx_next = -1;
 
   // Iteration t = -1 only fills the first tile; iteration t >= 0 runs tile t and, behind
   // its P.V product, fills tile t + 1.
@@ -544,23 +631,23 @@ sm100_attn_kernel(const AttnParams p) {
   for (int t = -1; t < n_tiles; ++t) {
     const bool more = t + 1 < n_tiles;
     if (t >= 0) {
-    if (tid == 0) issue_qk(t, ok);
+    if (tid == ISSUE_TID) issue_qk(t, ok);
     __syncwarp();
-    if (more) {
-      stage_load(stage, p, lv, tidx, upos, lv.begin + (t + 1) * TILE, 0, warp, lane);
-      fill_scales((t + 1) & 1, lv.begin + (t + 1) * TILE + row, ridx_next);   // read after the syncs below
+    if (t + 2 < n_tiles) {                       // list entries of the tile after next
+      const int j2 = lv.begin + (t + 2) * TILE;
+      tidx_next[0] = list_index<EXTRA>(lv, j2 + geo.row(0));
+      tidx_next[1] = list_index<EXTRA>(lv, j2 + geo.row(1));
+      ridx_n2 = list_index<EXTRA>(lv, j2 + row);
     }
-    if (tid == 0 && t > 0) TSTAMP(t, 6);
     // Is this thread's row masked (beyond the range, or an invalid entry under masking rules)?
     bool masked = true;
     {
       const int j = lv.begin + t * TILE + row;
       if (j < lv.end) {
-        const int ntok = (j < lv.len) ? p.n_tok : p.extra_n_tok;
-        masked = !(ridx >= 0 && ridx < ntok) && mask_invalid;
+        const int ntok = (EXTRA && j >= lv.len) ? p.extra_n_tok : p.n_tok;
+        masked = static_cast<unsigned>(ridx) >= static_cast<unsigned>(ntok) && mask_invalid;
       }
     }
-    ridx = ridx_next;
 
     if (ok && !mbar_wait_warp(bar_s_full, t & 1, lane)) { atomicExch(&g_attn_error, ERR_SFULL); ok = false; }
     tc_fence_after_sync();
@@ -571,12 +658,10 @@ sm100_attn_kernel(const AttnParams p) {
       uint32_t ra[16];
       tmem_ld16(tmem + tlane + COL_S + cg * 16, ra);
       tmem_ld_wait();
-      float cm = -INFINITY;
+      float v[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float m = warp_max_f32(masked ? -INFINITY : __uint_as_float(ra[i]));
-        cm = (lane == i) ? m : cm;
-      }
+      for (int i = 0; i < 16; ++i) v[i] = masked ? -INFINITY : __uint_as_float(ra[i]);
+      const float cm = warp_col_max16_bf16(v, lane);
       if (lane < 16) ctrl.wred[lg][cg * 16 + lane] = cm;
     }
     __syncthreads();
@@ -653,23 +738,26 @@ sm100_attn_kernel(const AttnParams p) {
     tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) mbar_arrive(bar_p_full);
-    if (tid == 0) {
-      TSTAMP(t, 4);
-      issue_pv(t, !more, ok);
-    }
+    if (tid == 0) TSTAMP(t, 4);
+    if (tid == ISSUE_TID) issue_pv(t, !more, ok);
     __syncwarp();
 
     }  // t >= 0
 
     // fill tile t + 1 (behind the P.V product of tile t, if there is one)
     if (more) {
-      refill(lv.begin + (t + 1) * TILE, t, (t + 1) & 1, ok);
-      if (t + 2 < n_tiles) {
-        index_load<FMT, DQK>(tidx, upos, lv, lv.begin + (t + 2) * TILE, warp, lane);
-        ridx_next = list_index(lv, lv.begin + (t + 2) * TILE + row);
-      }
+      refill(lv.begin + (t + 1) * TILE, t, (t + 1) & 1, t + 2 < n_tiles, ok);
       if (tid == 0) TSTAMP(t + 1, 0);
       if (tid == THREADS - 32) TSTAMP(t + 1, 7);
+    }
+    // The registers now hold (or are receiving) tile t + 2: publish its multipliers (read
+    // after the two CTA barriers of the next iteration).
+    tidx[0] = tidx_next[0];
+    tidx[1] = tidx_next[1];
+    if (t + 2 < n_tiles) fill_scales(t & 1, lv.begin + (t + 2) * TILE + row, ridx_n2);
+    if (t >= 0) {
+      ridx = ridx_n1;
+      ridx_n1 = ridx_n2;
     }
   }
 
@@ -739,7 +827,7 @@ sm100_attn_kernel(const AttnParams p) {
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
 }
 
-template <int FMT, int DQK>
+template <int FMT, int DQK, bool EXTRA>
 cudaError_t launch_one(const AttnParams& p, cudaStream_t st) {
   constexpr size_t smem = smem_bytes<FMT, DQK>();
   static bool configured = false;        // per process; the attribute is per function
@@ -747,7 +835,7 @@ cudaError_t launch_one(const AttnParams& p, cudaStream_t st) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (!configured || configured_dev != dev) {
-    cudaError_t e = cudaFuncSetAttribute(sm100_attn_kernel<FMT, DQK>,
+    cudaError_t e = cudaFuncSetAttribute(sm100_attn_kernel<FMT, DQK, EXTRA>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
     if (e) return e;
@@ -755,7 +843,7 @@ cudaError_t launch_one(const AttnParams& p, cudaStream_t st) {
     configured_dev = dev;
   }
   dim3 grid(p.n_req, (p.h_q + HEADS - 1) / HEADS, p.n_splits);
-  sm100_attn_kernel<FMT, DQK><<<grid, THREADS, smem, st>>>(p);
+  sm100_attn_kernel<FMT, DQK, EXTRA><<<grid, THREADS, smem, st>>>(p);
   return cudaGetLastError();
 }
 
@@ -767,10 +855,13 @@ bool sm100_attn_supported(int kv_format, int d_qk) {
 }
 
 cudaError_t launch_sm100_attn(const AttnParams& p, int kv_format, int d_qk, cudaStream_t st) {
-  if (kv_format == DSV4_KV_MODEL1) return launch_one<DSV4_KV_MODEL1, 512>(p, st);
-  if (kv_format == DSV4_KV_V32) return launch_one<DSV4_KV_V32, 576>(p, st);
-  if (d_qk == 512) return launch_one<DSV4_KV_BF16, 512>(p, st);
-  return launch_one<DSV4_KV_BF16, 576>(p, st);
+  const bool extra = p.extra_kv != nullptr;
+  if (kv_format == DSV4_KV_MODEL1)
+    return extra ? launch_one<DSV4_KV_MODEL1, 512, true>(p, st) : launch_one<DSV4_KV_MODEL1, 512, false>(p, st);
+  if (kv_format == DSV4_KV_V32)
+    return extra ? launch_one<DSV4_KV_V32, 576, true>(p, st) : launch_one<DSV4_KV_V32, 576, false>(p, st);
+  if (d_qk == 512) return launch_one<DSV4_KV_BF16, 512, false>(p, st);
+  return launch_one<DSV4_KV_BF16, 576, false>(p, st);
 }
 
 cudaError_t read_attn_error(int* value, bool reset) {
