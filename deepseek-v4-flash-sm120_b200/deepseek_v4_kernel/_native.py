@@ -62,6 +62,7 @@ SYMBOLS = {
                                    C.POINTER(C.c_int)]),
     "dsv4_plan_splits": (C.c_int, [C.c_int] * 6),
     "dsv4_sparse_decode": (C.c_int, [C.POINTER(DecodeArgs), vp]),
+    "dsv4_sparse_decode_noalloc": (C.c_int, [C.POINTER(DecodeArgs), vp]),
     "dsv4_split_combine": (C.c_int, [C.POINTER(CombineArgs), vp]),
     "dsv4_sparse_prefill": (C.c_int, [C.POINTER(PrefillArgs), vp]),
     "dsv4_kv_store": (C.c_int, [C.POINTER(StoreArgs), vp]),

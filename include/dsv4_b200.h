@@ -31,7 +31,8 @@ enum Dsv4Status {
   DSV4_ERR_ARCH = 5,        /* the current device is not sm_100                */
   DSV4_ERR_CUDA = 6,        /* a CUDA runtime call failed (see dsv4_last_cuda_error) */
   DSV4_ERR_SCRATCH = 7,     /* n_splits > 1 but scratch pointers are null      */
-  DSV4_ERR_UNSUPPORTED = 8  /* valid request that this build does not implement */
+  DSV4_ERR_UNSUPPORTED = 8, /* valid request that this build does not implement */
+  DSV4_ERR_SCRATCH_TOO_LARGE = 9 /* dsv4_sparse_decode_noalloc: partials exceed the built-in scratch */
 };
 
 /* KV-cache token layouts.  A page of P tokens is two sections:
@@ -108,6 +109,35 @@ typedef struct Dsv4DecodeArgs {
 } Dsv4DecodeArgs;
 
 int dsv4_sparse_decode(const Dsv4DecodeArgs* args, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------
+ * Sparse decode without any allocation.  No counterpart in the reference (its
+ * host code allocates the split-KV partials on every call,
+ * csrc/api/sparse_decode.cpp:176-182).
+ *
+ * For callers that cannot obtain device memory at call time: code running under
+ * CUDA-graph capture or replay, code inside another runtime's no-allocation /
+ * no-synchronisation sections, embedders without an allocator.  Same arguments
+ * and results as dsv4_sparse_decode, except that args->o_accum / lse_accum are
+ * ignored: the split-KV partials go to a fixed array inside the library's device
+ * image (DSV4_NOALLOC_MAX_O_FLOATS fp32 values of partial output plus one
+ * log-sum-exp per 512 of them, about 16 MiB, held by every GPU that loads the
+ * library until the process exits).  The call performs no cudaMalloc / cudaFree
+ * and uses no allocating library routine.
+ *
+ *  - Limit: n_splits * b * s_q * h_q * 512 <= DSV4_NOALLOC_MAX_O_FLOATS when
+ *    n_splits > 1 (batch 16 x 64 heads x 8 splits fits exactly); larger requests
+ *    return DSV4_ERR_SCRATCH_TOO_LARGE and launch nothing.
+ *  - The FIRST call on each device looks up the array's device address (a cheap,
+ *    one-time query with that device current).  Make that first call before any
+ *    stream capture begins.
+ *  - All calls on a device share the one array and it keeps whatever the last
+ *    call left in it.  Nothing needs clearing (each call writes every slot it
+ *    later reads), but two calls whose kernels overlap on the GPU (different
+ *    streams, or graph branches) race on it: serialise them.
+ * ------------------------------------------------------------------------- */
+#define DSV4_NOALLOC_MAX_O_FLOATS 4194304
+int dsv4_sparse_decode_noalloc(const Dsv4DecodeArgs* args, void* cuda_stream);
 
 /* Split count for a decode call: a pure function of shapes and the SM count, so
  * it is stable under CUDA-graph capture.  Stands in for the heuristic at
