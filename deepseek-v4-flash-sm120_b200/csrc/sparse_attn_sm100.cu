@@ -72,8 +72,9 @@ template <int FMT, int DQK> struct Cfg {
   static constexpr int K_BYTES = NB * KBLOCK_BYTES;
   static constexpr int Q_BYTES = NB * QBLOCK_BYTES;
   static constexpr int P_BYTES = P_ALIAS ? 0 : TILE * 128;
-  // words per tile row in the multiplier table: V32 has 4 scale bytes, MODEL1 7 (padded to 8)
-  static constexpr int MUL_PER_ROW = !PAGED ? 0 : (DQK == 576 ? 4 : 8);
+  // words per tile row in the multiplier table: a (first, second) factor pair per scale
+  // byte; V32 has 4 scale bytes, MODEL1 7 (padded to 8)
+  static constexpr int MUL_PER_ROW = !PAGED ? 0 : (DQK == 576 ? 8 : 16);
   static constexpr int MUL_TAB_BYTES = 2 * TILE * MUL_PER_ROW * 4;      // double-buffered
 };
 
@@ -85,7 +86,6 @@ struct Ctrl {
   int fail;
   float wred[4][HEADS];                // per-lane-group column partials (max, then sums)
   float mref[HEADS];                   // reference max, log2-scaled units
-  float muse[HEADS];                   // mref with -inf replaced by 0 (exponent offset)
   float mtrue[HEADS];                  // true running max, log2-scaled units
   float alpha[HEADS];                  // rescale factor / final output factor
 };
@@ -171,8 +171,14 @@ __device__ __forceinline__ float warp_col_max16_bf16(const float (&v)[16], int l
 }
 
 // Debug timeline: SM cycle counter of CTA (0,0,0) into p.prof[slot] when a buffer is set.
+// Compiled in only with -DDSV4_TIMELINE (the stamps cost instructions in the hot loop).
 __device__ __forceinline__ void stamp(const AttnParams& p, int slot) {
+#ifdef DSV4_TIMELINE
   if (p.prof != nullptr && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) p.prof[slot] = clock64();
+#else
+  (void)p;
+  (void)slot;
+#endif
 }
 constexpr int PROF_TILE0 = 8, PROF_PER_TILE = 8, PROF_MAX_TILES = 15;
 
@@ -279,23 +285,12 @@ __device__ __forceinline__ void load_half(uint4 (&d)[Stage<FMT, DQK>::LINES], co
   }
 }
 
-// Raw scale byte `sb` of token idx; used only where the multiplier table holds 0.
-template <int FMT>
-static __device__ __noinline__ uint32_t rare_scale_byte(const uint8_t* kv, int64_t stride, int ntok,
-                                                        int pb, int sh, int idx, int sb) {
-  const CacheSel c{kv, stride, ntok, pb, sh};
-  const uint8_t* scl;
-  const uint8_t* r = row_ptr<FMT>(c, idx, scl);
-  return r != nullptr ? scl[sb] : 0x7fu;
-}
-
-// Convert and store line C of the staged row `v` (tile row `row`).  `mul_row` points at
-// the row's entries of the multiplier table: one packed-BF16 factor 2^(s-7) per scale
-// byte s, or 0 where s needs the two-factor path (s = 0 or s > 134).
-template <int FMT, int DQK, int LINE, class RawScale>
+// Convert and store line LINE of the staged row `v` (tile row `row`).  `mul_row` holds the
+// row's entries of the multiplier table: per scale byte s a pair of packed-BF16 factors,
+// (2^(s-7), 0) normally, (2^120, 2^(s-127)) for s = 0 or s > 134.
+template <int FMT, int DQK, int LINE>
 __device__ __forceinline__ void store_line(const uint4& v, uint32_t sK, int row, int piece,
-                                           const uint32_t (&mul_row)[Cfg<FMT, DQK>::MUL_PER_ROW + 1],
-                                           RawScale raw_scale) {
+                                           const uint32_t (&mul_row)[Cfg<FMT, DQK>::MUL_PER_ROW + 2]) {
   using S = Stage<FMT, DQK>;
   using C = Cfg<FMT, DQK>;
   const int x = row & 7;
@@ -305,22 +300,20 @@ __device__ __forceinline__ void store_line(const uint4& v, uint32_t sK, int row,
     using T = KvTraits<FMT>;
     constexpr bool ALL_FP8 = 8 * LINE + 7 < S::FP8_CH, NO_FP8 = 8 * LINE >= S::FP8_CH;
     if (ALL_FP8 || (!NO_FP8 && ci < S::FP8_CH)) {
-      const int sb = ci * 16 / T::TILE;                         // scale byte of this chunk
-      uint32_t c1;
-      if constexpr (T::TILE == 128) c1 = mul_row[LINE];         // 8 chunks per scale tile
-      else c1 = (piece & 4) ? mul_row[2 * LINE + 1] : mul_row[2 * LINE];
-      uint32_t c2 = 0;
-      if (c1 == 0) {                                            // rare
-        const ScaleMul m = make_scale_mul(raw_scale(sb));
-        c1 = m.c1;
-        c2 = m.c2;
+      uint32_t c1, c2;
+      if constexpr (T::TILE == 128) {                           // 8 chunks per scale tile
+        c1 = mul_row[2 * LINE];
+        c2 = mul_row[2 * LINE + 1];
+      } else {                                                  // 4 chunks per scale tile
+        c1 = (piece & 4) ? mul_row[4 * LINE + 2] : mul_row[4 * LINE];
+        c2 = (piece & 4) ? mul_row[4 * LINE + 3] : mul_row[4 * LINE + 1];
       }
       uint32_t o[8];
       dequant4_one_mul(v.x, c1, o[0], o[1]);
       dequant4_one_mul(v.y, c1, o[2], o[3]);
       dequant4_one_mul(v.z, c1, o[4], o[5]);
       dequant4_one_mul(v.w, c1, o[6], o[7]);
-      if (c2 != 0) {
+      if (c2 != 0) {                                            // rare scale bytes
 #pragma unroll
         for (int k = 0; k < 8; ++k) o[k] = bf16x2_mul(o[k], c2);
       }
@@ -337,14 +330,13 @@ __device__ __forceinline__ void store_line(const uint4& v, uint32_t sK, int row,
   }
 }
 
-template <int FMT, int DQK, int LINE, class RawScale>
+template <int FMT, int DQK, int LINE>
 __device__ __forceinline__ void store_lines(const uint4 (&d)[Stage<FMT, DQK>::LINES], uint32_t sK,
                                             int row, int piece,
-                                            const uint32_t (&mul_row)[Cfg<FMT, DQK>::MUL_PER_ROW + 1],
-                                            RawScale raw_scale) {
+                                            const uint32_t (&mul_row)[Cfg<FMT, DQK>::MUL_PER_ROW + 2]) {
   if constexpr (LINE < Stage<FMT, DQK>::LINES) {
-    store_line<FMT, DQK, LINE>(d[LINE], sK, row, piece, mul_row, raw_scale);
-    store_lines<FMT, DQK, LINE + 1>(d, sK, row, piece, mul_row, raw_scale);
+    store_line<FMT, DQK, LINE>(d[LINE], sK, row, piece, mul_row);
+    store_lines<FMT, DQK, LINE + 1>(d, sK, row, piece, mul_row);
   }
 }
 
@@ -452,9 +444,9 @@ sm100_attn_kernel(const AttnParams p) {
         uint32_t* dst = mul_tab + (slot * TILE + tid) * C::MUL_PER_ROW;
 #pragma unroll
         for (int k = 0; k < T::N_SCALE; ++k) {
-          const uint32_t sbyte = (w[k >> 2] >> (8 * (k & 3))) & 0xffu;
-          const uint32_t c = (sbyte + 120u) << 7;
-          dst[k] = (sbyte >= 1 && sbyte <= 134) ? (c | (c << 16)) : 0u;
+          const ScaleMul m = make_scale_mul((w[k >> 2] >> (8 * (k & 3))) & 0xffu);
+          dst[2 * k] = m.c1;
+          dst[2 * k + 1] = m.c2;
         }
       }
     }
@@ -474,7 +466,6 @@ sm100_attn_kernel(const AttnParams p) {
   }
   if (tid < HEADS) {
     ctrl.mref[tid] = -INFINITY;
-    ctrl.muse[tid] = 0.f;
     ctrl.mtrue[tid] = -INFINITY;
     ctrl.alpha[tid] = 1.f;
   }
@@ -538,24 +529,22 @@ sm100_attn_kernel(const AttnParams p) {
     if (ok && !mbar_wait(bar_k_full, t & 1)) { atomicExch(&g_attn_error, ERR_KFULL); ok = false; }
     tc_fence_after_sync();
     TSTAMP(t, 1);
-#pragma unroll
+#pragma unroll 1
     for (int kb = 0; kb < C::NB; ++kb)       // four 16-wide steps of one 64-column block
       umma_bf16_x4(tmem + COL_S, 0, dK_lo + ((kb * KBLOCK_BYTES) >> 4), dK_hi, 2,
                    dQ_lo + ((kb * QBLOCK_BYTES) >> 4), dQ_hi, 2, idesc_qk, kb != 0, 1);
-    if (t == 3) stamp(p, 130 + C::NB);
     umma_commit(bar_s_full);
   };
   auto issue_pv = [&](int t, bool last, bool& ok) {
     if (ok && !mbar_wait(bar_p_full, t & 1)) { atomicExch(&g_attn_error, ERR_PFULL); ok = false; }
     tc_fence_after_sync();
     TSTAMP(t, 5);
-#pragma unroll
+#pragma unroll 1
     for (int j = 0; j < KSTEPS; ++j) {       // the four 128-row slices of O^T for one k-step
       const uint32_t acc = (t | j) != 0;
       umma_bf16_x4(tmem + COL_O, HEADS, dV_lo + ((j * 2048) >> 4), dV_hi, (2 * KBLOCK_BYTES) >> 4,
                    dP_lo + ((j * 2048) >> 4), dP_hi, 0, idesc_pv, acc, acc);
       umma_commit(bar_kv_free0 + 8 * j);
-      if (t == 3) stamp(p, 140 + j);
     }
     if (last) umma_commit(bar_o_done);
   };
@@ -577,7 +566,7 @@ sm100_attn_kernel(const AttnParams p) {
         atomicExch(&g_attn_error, ERR_KVFREE);
         ok = false;
       }
-      uint32_t mrow[C::MUL_PER_ROW + 1];          // the row's multipliers, one vector load each 4
+      uint32_t mrow[C::MUL_PER_ROW + 2];          // the row's multipliers, one vector load each 4
       if constexpr (C::PAGED) {
         const uint4* src = reinterpret_cast<const uint4*>(mul_tab + (slot * TILE + trow) * C::MUL_PER_ROW);
 #pragma unroll
@@ -586,13 +575,8 @@ sm100_attn_kernel(const AttnParams p) {
           mrow[4 * k] = m4.x; mrow[4 * k + 1] = m4.y; mrow[4 * k + 2] = m4.z; mrow[4 * k + 3] = m4.w;
         }
       }
-      mrow[C::MUL_PER_ROW] = 0;
-      store_lines<FMT, DQK, 0>(stage.d[hh], sK, trow, geo.piece, mrow,
-                               [&](int sb) -> uint32_t {
-        const CacheSel c = cache_of<EXTRA>(p, lv, j0 + trow);
-        return rare_scale_byte<C::PAGED ? FMT : DSV4_KV_V32>(c.kv, c.stride, c.ntok, c.pb, c.sh,
-                                                             tidx[jhalf], sb);
-      });
+      mrow[C::MUL_PER_ROW] = mrow[C::MUL_PER_ROW + 1] = 0;
+      store_lines<FMT, DQK, 0>(stage.d[hh], sK, trow, geo.piece, mrow);
       if (jhalf == 1) {                    // tile complete: publish before reloading
         fence_async_smem();
         __syncwarp();
@@ -674,7 +658,6 @@ sm100_attn_kernel(const AttnParams p) {
       if (tm > mr + RESCALE_THRESHOLD) {                 // also the first finite max
         alpha = (mr == -INFINITY) ? 0.f : ex2(mr - tm);
         ctrl.mref[tid] = tm;
-        ctrl.muse[tid] = tm;
         ctrl.resc[t & 1] = 1;
       }
       ctrl.alpha[tid] = alpha;
@@ -716,7 +699,11 @@ sm100_attn_kernel(const AttnParams p) {
       uint32_t pk[8];
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
-        const float4 mu = *reinterpret_cast<const float4*>(&ctrl.muse[cg * 16 + q4 * 4]);
+        float4 mu = *reinterpret_cast<const float4*>(&ctrl.mref[cg * 16 + q4 * 4]);
+        mu.x = (mu.x == -INFINITY) ? 0.f : mu.x;      // nothing seen yet: any finite offset will do
+        mu.y = (mu.y == -INFINITY) ? 0.f : mu.y;
+        mu.z = (mu.z == -INFINITY) ? 0.f : mu.z;
+        mu.w = (mu.w == -INFINITY) ? 0.f : mu.w;
         const float p0 = ex2(fmaf(__uint_as_float(s[q4 * 4 + 0]), cs, -mu.x));
         const float p1 = ex2(fmaf(__uint_as_float(s[q4 * 4 + 1]), cs, -mu.y));
         const float p2 = ex2(fmaf(__uint_as_float(s[q4 * 4 + 2]), cs, -mu.z));
@@ -802,7 +789,7 @@ sm100_attn_kernel(const AttnParams p) {
   if (!ctrl.fail) {
     const int m = warp >> 2;
     const int d = m * 128 + lg * 32 + lane;
-#pragma unroll
+#pragma unroll 1
     for (int c4 = 0; c4 < HEADS / 16; ++c4) {
       uint32_t o[16];
       tmem_ld16(tmem + tlane + COL_O + m * HEADS + c4 * 16, o);

@@ -246,7 +246,8 @@ int dsv4_device_status(int32_t* status_out, int reset);
 
 /* Debug aid: give the attention kernels a device buffer of >= 128 int64 into
  * which CTA (0,0,0) of every later launch writes SM cycle-counter stamps of its
- * pipeline stages (null switches it off).  Process-wide; not for production.           */
+ * pipeline stages (null switches it off).  Process-wide; not for production.  The
+ * stamps exist only in a library built with -DDSV4_TIMELINE; otherwise this is a no-op. */
 int dsv4_debug_set_timeline(void* device_buffer);
 
 /* Text for a status code; the last CUDA error string seen by this thread.             */
