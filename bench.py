@@ -57,55 +57,86 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a
-    timed region runs (read-only query)."""
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    """Samples the SM clock and the throttle reasons of one GPU while a timed region runs
+    (read-only queries: NVML in a thread, or an `nvidia-smi -lms` child when NVML cannot be
+    loaded).  The GPU is found by UUID so CUDA_VISIBLE_DEVICES remapping cannot pick another."""
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    SMI_FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+                  "clocks_event_reasons.hw_thermal_slowdown,"
+                  "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, device: torch.device, period_s: float = 0.005):
+        self.uuid = "GPU-" + str(torch.cuda.get_device_properties(device).uuid)
+        self.period, self.rows, self.stop = period_s, [], threading.Event()
+        self.thread, self.proc, self.source = None, None, None
+
+    def _nvml_loop(self, nv, h):
+        bits = [(nv.nvmlClocksEventReasonHwSlowdown, "hw_slowdown"),
+                (nv.nvmlClocksEventReasonHwThermalSlowdown, "hw_thermal_slowdown"),
+                (nv.nvmlClocksEventReasonSwThermalSlowdown, "sw_thermal_slowdown"),
+                (nv.nvmlClocksEventReasonSwPowerCap, "sw_power_cap")]
+        mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+        while not self.stop.is_set():
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                self.rows.append((float(sm), float(mx), [n for b, n in bits if mask & b]))
+            except Exception:  # noqa: BLE001
+                pass
+            self.stop.wait(self.period)
+
+    def _smi_loop(self):
+        for line in self.proc.stdout:
+            c = [x.strip() for x in line.split(",")]
+            try:
+                self.rows.append((float(c[0]), float(c[1]),
+                                  [n for n, v in zip(self.NAMES, c[2:6])
+                                   if v.lower().startswith("active")]))
+            except Exception:  # noqa: BLE001
+                continue
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "50"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByUUID(self.uuid)
+            nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, h), daemon=True)
+            self.source = "nvml"
         except Exception:  # noqa: BLE001
-            self.proc = None
+            try:
+                self.proc = subprocess.Popen(
+                    ["nvidia-smi", "-i", self.uuid, f"--query-gpu={self.SMI_FIELDS}",
+                     "--format=csv,noheader,nounits", "-lms", "50"],
+                    stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                self.thread = threading.Thread(target=self._smi_loop, daemon=True)
+                self.source = "nvidia-smi"
+            except Exception:  # noqa: BLE001
+                self.thread = None
+        if self.thread is not None:
+            self.thread.start()
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
-
     def __exit__(self, *exc):
+        self.stop.set()
         if self.proc is not None:
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
             except Exception:  # noqa: BLE001
                 self.proc.kill()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            try:
-                sm.append(float(r[0]))
-                mx.append(float(r[1]))
-                for n, v in zip(names, r[2:6]):
-                    if v.lower().startswith("active"):
-                        reasons.add(n)
-            except Exception:  # noqa: BLE001
-                continue
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm)}
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0,
+                    "source": self.source}
+        reasons = sorted({n for r in self.rows for n in r[2]})
+        return {"sm_mhz": statistics.median(r[0] for r in self.rows),
+                "sm_min_mhz": min(r[0] for r in self.rows),
+                "sm_max_mhz": max(r[1] for r in self.rows), "reasons": reasons,
+                "samples": len(self.rows), "source": self.source}
 
 
 def dist_env():
@@ -228,28 +259,47 @@ def run_ours(args):
         step(i)
     barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
+
+    def same_load(seconds: float, i0: int):
+        """Untimed steps of the same loop, so the clock samples bracket the timed region
+        under the load it runs at (the region alone can be shorter than one sample)."""
+        t_end, i = time.perf_counter() + seconds, i0
+        while time.perf_counter() < t_end:
+            for _ in range(64):
+                step(i)
+                i += 1
+            stream.synchronize()
+        return i
+
+    with ClockSampler(dev) as clocks:
+        same_load(args.clock_window / 2, args.warmup)
+        barrier()
         ev0.record(stream)
         for i in range(args.steps):
             step(i)
         ev1.record(stream)
         barrier()
+        same_load(args.clock_window / 2, 0)
+        barrier()
     ms_total = max_over_ranks(ev0.elapsed_time(ev1))
     ms_per_step = ms_total / args.steps
     value = world * mean_bytes / (ms_per_step * 1e-3) / 1e9
 
-    # ---- (2) decode kernel alone, per launch (events between the two kernels) -------
-    n_k = min(args.steps, 64)
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-           for _ in range(n_k)]
+    # ---- (2) the decode kernel alone: back-to-back launches without the combine ------
+    # (the partials of one launch are overwritten by the next; one event pair around the
+    # whole run, so no per-launch event overhead is counted as kernel time)
+    n_k = max(args.steps, 50)
+    for i in range(3):
+        call.decode(stream.cuda_stream, with_combine=False)
+    barrier()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record(stream)
     for i in range(n_k):
         call.set_indices(wl.indices[i % N_INDEX_SETS])
-        evs[i][0].record(stream)
         call.decode(stream.cuda_stream, with_combine=False)
-        evs[i][1].record(stream)
-        call.combine(stream.cuda_stream)
+    k1.record(stream)
     torch.cuda.synchronize(dev)
-    k_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+    k_ms = k0.elapsed_time(k1) / n_k
     peak, peak_src = measured_peaks()
     achieved = mean_bytes / (k_ms * 1e-3) / 1e9
 
@@ -372,6 +422,9 @@ def main():
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--extras", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--clock-window", type=float, default=1.0,
+                    help="seconds of identical untimed load around the timed region over which "
+                         "SM clocks are sampled")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

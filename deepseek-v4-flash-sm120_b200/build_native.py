@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
-OUT = os.path.join(HERE, "deepseek_v4_kernel", "libdsv4_b200.so")
+OUT = os.environ.get("DSV4_BUILD_OUT") or os.path.join(HERE, "deepseek_v4_kernel", "libdsv4_b200.so")
 SOURCES = ["capi.cu", "simple_kernels.cu", "umma_selftest.cu", "sparse_attn_sm100.cu",
            "noalloc_entry.cu"]
 

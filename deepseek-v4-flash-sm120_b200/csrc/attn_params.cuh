@@ -6,6 +6,16 @@
 
 namespace dsv4 {
 
+// Programmatic dependent launch (see add_overlap_attribute): block until the kernel before
+// this one in the stream has completed and its writes are visible / allow the kernel after
+// this one to be set up.  Both are no-ops when the launch carries no such dependency.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 enum AttnMode : int { MODE_DECODE = 0, MODE_PREFILL = 1 };
 
 constexpr int SPLIT_GRANULE = 16;    // split ranges are multiples of 16 list entries

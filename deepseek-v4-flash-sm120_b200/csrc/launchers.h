@@ -5,9 +5,27 @@
 
 #include "dsv4_b200.h"
 
+#include <cstdlib>
+
 namespace dsv4 {
 
 struct AttnParams;
+
+// Programmatic dependent launch: with this attribute a kernel may be set up on the SMs
+// while the kernel before it in the stream is still in its last phase; both kernels here
+// execute griddepcontrol.wait before their first global access, so they still observe all
+// of the predecessor's writes.  DSV4_NO_PDL=1 turns the attribute off.
+// Returns the number of attributes written (0 or 1).
+inline int add_overlap_attribute(cudaLaunchAttribute* attr) {
+  static const bool off = [] {
+    const char* e = std::getenv("DSV4_NO_PDL");
+    return e != nullptr && e[0] != '\0' && e[0] != '0';
+  }();
+  if (off) return 0;
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  return 1;
+}
 
 // CUDA-core cross-check kernels (simple_kernels.cu).
 cudaError_t launch_simple_attn(const AttnParams& p, int kv_format, int d_qk, cudaStream_t st);

@@ -164,12 +164,18 @@ simple_attn_kernel(AttnParams p) {
 // ---------------------------------------------------------------------------
 constexpr int COMBINE_WARPS = 8;
 constexpr int COMBINE_MAX_SPLITS = 256;
+constexpr int COMBINE_PARTS = 4;          // warps sharing one (row, head): 128 columns each
+constexpr int COMBINE_BATCH = 8;          // partial rows in flight per thread
 
+// Warp (row, head, part) merges columns [128 part, 128 part + 128) of the n_splits partial
+// rows: every lane owns one float4 per split and keeps COMBINE_BATCH loads in flight.
 __global__ void __launch_bounds__(COMBINE_WARPS * 32)
 combine_kernel(Dsv4CombineArgs a) {
   __shared__ float s_w[COMBINE_WARPS][COMBINE_MAX_SPLITS];
+  grid_dependency_wait();                 // the partials come from the kernel just before
   const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y * COMBINE_WARPS + warp;
+  const int unit = blockIdx.y * COMBINE_WARPS + warp;
+  const int h = unit / COMBINE_PARTS, part = unit % COMBINE_PARTS;
   if (h >= a.h_q) return;
   const int64_t rows_h = static_cast<int64_t>(a.n_rows) * a.h_q;
   const int64_t slot0 = static_cast<int64_t>(row) * a.h_q + h;
@@ -192,35 +198,36 @@ combine_kernel(Dsv4CombineArgs a) {
   const float f = finalize_row(MODE_DECODE, m, l, has_sink, has_sink ? a.attn_sink[h] : 0.f,
                                lse_v, ml_v);
   const int bi = row / a.s_q, si = row % a.s_q;
-  if (lane == 0) a.lse[bi * a.stride_lse_b + si * a.stride_lse_s + h * a.stride_lse_h] = lse_v;
+  if (lane == 0 && part == 0)
+    a.lse[bi * a.stride_lse_b + si * a.stride_lse_s + h * a.stride_lse_h] = lse_v;
 
-  float acc[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-  const float4* src = reinterpret_cast<const float4*>(a.o_accum + slot0 * D_V) + lane;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4* src = reinterpret_cast<const float4*>(a.o_accum + slot0 * D_V) + part * 32 + lane;
   const int64_t split_stride4 = rows_h * D_V / 4;
-  for (int s = 0; s < a.n_splits; ++s) {
-    const float w = s_w[warp][s];
-    if (w == 0.f) continue;
-    const float4* ps = src + s * split_stride4;
+  for (int s0 = 0; s0 < a.n_splits; s0 += COMBINE_BATCH) {
+    float4 v[COMBINE_BATCH];
+    float w[COMBINE_BATCH];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float4 v = __ldg(ps + i * 32);
-      acc[4 * i + 0] = fmaf(w, v.x, acc[4 * i + 0]);
-      acc[4 * i + 1] = fmaf(w, v.y, acc[4 * i + 1]);
-      acc[4 * i + 2] = fmaf(w, v.z, acc[4 * i + 2]);
-      acc[4 * i + 3] = fmaf(w, v.w, acc[4 * i + 3]);
+    for (int k = 0; k < COMBINE_BATCH; ++k) {
+      const int s = s0 + k;
+      w[k] = s < a.n_splits ? s_w[warp][s] : 0.f;
+      v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (w[k] != 0.f) v[k] = __ldg(src + s * split_stride4);
+    }
+#pragma unroll
+    for (int k = 0; k < COMBINE_BATCH; ++k) {       // fixed order: the result does not depend on timing
+      acc.x = fmaf(w[k], v[k].x, acc.x);
+      acc.y = fmaf(w[k], v[k].y, acc.y);
+      acc.z = fmaf(w[k], v[k].z, acc.z);
+      acc.w = fmaf(w[k], v[k].w, acc.w);
     }
   }
   __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(a.out) + bi * a.stride_o_b +
                         si * a.stride_o_s + h * a.stride_o_h;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    __nv_bfloat162 lo = __floats2bfloat162_rn(acc[4 * i] * f, acc[4 * i + 1] * f);
-    __nv_bfloat162 hi = __floats2bfloat162_rn(acc[4 * i + 2] * f, acc[4 * i + 3] * f);
-    uint2 v = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-    *reinterpret_cast<uint2*>(orow + (i * 32 + lane) * 4) = v;
-  }
+  __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * f, acc.y * f);
+  __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * f, acc.w * f);
+  *reinterpret_cast<uint2*>(orow + (part * 32 + lane) * 4) =
+      make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
 }
 
 // ---------------------------------------------------------------------------
@@ -343,9 +350,14 @@ cudaError_t launch_simple_attn(const AttnParams& p, int kv_format, int d_qk, cud
 }
 
 cudaError_t launch_combine(const Dsv4CombineArgs& a, cudaStream_t st) {
-  dim3 grid(a.n_rows, (a.h_q + COMBINE_WARPS - 1) / COMBINE_WARPS);
-  combine_kernel<<<grid, COMBINE_WARPS * 32, 0, st>>>(a);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(a.n_rows, (a.h_q * COMBINE_PARTS + COMBINE_WARPS - 1) / COMBINE_WARPS);
+  cfg.blockDim = dim3(COMBINE_WARPS * 32);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  cfg.attrs = attr;
+  cfg.numAttrs = add_overlap_attribute(attr);
+  return cudaLaunchKernelEx(&cfg, combine_kernel, a);
 }
 
 int combine_max_splits() { return COMBINE_MAX_SPLITS; }

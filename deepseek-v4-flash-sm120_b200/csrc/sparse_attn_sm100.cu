@@ -61,6 +61,7 @@ constexpr float RESCALE_THRESHOLD = 8.0f;             // log2 units
 // The thread that issues the MMAs: lane 0 of the last warp, whose share of the K tile is
 // released last by the P.V product, so that the (blocking) issue delays no refill.
 constexpr int ISSUE_TID = THREADS - 32;
+constexpr int ISSUE_WARP = ISSUE_TID / 32;
 
 enum ErrCode { ERR_KFULL = 1, ERR_PFULL = 2, ERR_SFULL = 3, ERR_KVFREE = 4, ERR_ODONE = 5 };
 
@@ -110,8 +111,17 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
                "r"(d));
 }
 
+// 16 bytes of a KV row.  The rows are read once, so they are not kept in L1 (its array is
+// the one the tensor core reads its operands from).
 __device__ __forceinline__ uint4 ldg16(const uint8_t* p) {
-  return __ldg(reinterpret_cast<const uint4*>(p));
+  uint4 v;
+#ifdef DSV4_LDG_ALLOCATE
+  v = __ldg(reinterpret_cast<const uint4*>(p));
+#else
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+#endif
+  return v;
 }
 
 // Column-wise reduction, over the 32 lanes of a warp, of a 16-column slice held
@@ -181,6 +191,21 @@ __device__ __forceinline__ void stamp(const AttnParams& p, int slot) {
 #endif
 }
 constexpr int PROF_TILE0 = 8, PROF_PER_TILE = 8, PROF_MAX_TILES = 15;
+// Per-CTA wall-clock stamps (global timer, ns) at slots 256 + 4 * cta + k; the buffer holds
+// 256 + 4 * CTAs values.
+__device__ __forceinline__ void stamp_cta(const AttnParams& p, int k) {
+#ifdef DSV4_TIMELINE
+  if (p.prof != nullptr) {
+    const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    p.prof[256 + 4 * cta + k] = static_cast<long long>(t);
+  }
+#else
+  (void)p;
+  (void)k;
+#endif
+}
 
 struct ListView {
   const int32_t* main_idx;
@@ -204,8 +229,12 @@ __device__ __forceinline__ int list_index(const ListView& lv, int j) {
 // Register staging of one tile.  A tile is 8 "k-steps" of 16 rows (the rows one
 // P.V MMA step contracts over).  Warp w owns, in the two k-steps j = (w >> 2) and
 // j = 4 + (w >> 2), the four rows 4 * (w & 3) .. +4: lane l holds, for each
-// 128-byte line c of a row, the 16-byte chunk 8 c + (l & 7) of row (l >> 3).
-// So a warp-wide load touches four cache lines, the line number is a
+// 128-byte line c of a row, one 16-byte chunk of row (l & 1) + 2 (l >> 4).  The eight
+// lanes that a 128-bit shared-memory store handles together thus belong to two rows whose
+// swizzle patterns differ in the lowest bit, and the chunk a lane takes within a line is
+// chosen (differently for converted and for copied lines) so that those eight lanes hit
+// eight different 16-byte bank groups: no store is replayed.
+// A warp-wide load touches four cache lines, the line number is a
 // compile-time constant of every load/convert/store (addresses reduce to a
 // per-thread base plus an immediate), and a warp needs two list entries and two
 // waits per tile.  When P.V retires k-step j the four warps owning it refill it;
@@ -223,14 +252,17 @@ template <int FMT, int DQK> struct Stage {
   static constexpr int LINES = (CH + 7) / 8;
   static constexpr int PHASES = C::PAGED ? 1 : 2;
   static constexpr int HALVES = 2 / PHASES;                // k-steps held in registers at once
+  // Line c holds no FP8 chunk (it is copied, not converted).
+  __host__ __device__ static constexpr bool copied_line(int c) { return 8 * c >= FP8_CH; }
   uint4 d[HALVES][LINES];
 };
 
 // Per-thread constants of the staging geometry.
 struct Geo {
   int jsub;     // k-steps handled: jsub and 4 + jsub
-  int rloc;     // row within a k-step: 4 * (w & 3) + (l >> 3)
-  int piece;    // 16-byte chunk within a line: l & 7
+  int rloc;     // row within a k-step: 4 * (w & 3) + (l & 1) + 2 * (l >> 4)
+  int piece;    // 16-byte chunk within a converted (FP8) line; it is stored as two chunks
+  int piece_cp; // 16-byte chunk within a line that is copied as it is
   __device__ __forceinline__ int row(int jhalf) const { return 16 * (4 * jhalf + jsub) + rloc; }
 };
 
@@ -272,27 +304,40 @@ __device__ __forceinline__ const uint8_t* row_ptr(const CacheSel& c, int idx, co
 // idx) into one register set.
 template <int FMT, int DQK, bool EXTRA>
 __device__ __forceinline__ void load_half(uint4 (&d)[Stage<FMT, DQK>::LINES], const AttnParams& p,
-                                          const ListView& lv, int j, int idx, int piece) {
+                                          const ListView& lv, int j, int idx, const Geo& geo) {
   using S = Stage<FMT, DQK>;
   const uint8_t* scl;
   const uint8_t* row = row_ptr<FMT>(cache_of<EXTRA>(p, lv, j), idx, scl);
-  const uint8_t* src = row + 16 * piece;
 #pragma unroll
   for (int c = 0; c < S::LINES; ++c) {
+    const int piece = S::copied_line(c) ? geo.piece_cp : geo.piece;
     d[c] = make_uint4(0, 0, 0, 0);
     const bool in_row = (8 * c + 7 < S::CH) || (8 * c + piece < S::CH);
-    if (row != nullptr && in_row) d[c] = ldg16(src + 128 * c);
+    if (row != nullptr && in_row) d[c] = ldg16(row + 16 * piece + 128 * c);
   }
+}
+
+// One line of a row only (line number known at run time; warp-uniform).
+template <int FMT, int DQK, bool EXTRA>
+__device__ __forceinline__ void load_one_line(uint4& d, int line, const AttnParams& p,
+                                              const ListView& lv, int j, int idx, const Geo& geo) {
+  using S = Stage<FMT, DQK>;
+  const uint8_t* scl;
+  const uint8_t* row = row_ptr<FMT>(cache_of<EXTRA>(p, lv, j), idx, scl);
+  const int piece = S::copied_line(line) ? geo.piece_cp : geo.piece;
+  d = make_uint4(0, 0, 0, 0);
+  if (row != nullptr && 8 * line + piece < S::CH) d = ldg16(row + 16 * piece + 128 * line);
 }
 
 // Convert and store line LINE of the staged row `v` (tile row `row`).  `mul_row` holds the
 // row's entries of the multiplier table: per scale byte s a pair of packed-BF16 factors,
 // (2^(s-7), 0) normally, (2^120, 2^(s-127)) for s = 0 or s > 134.
 template <int FMT, int DQK, int LINE>
-__device__ __forceinline__ void store_line(const uint4& v, uint32_t sK, int row, int piece,
+__device__ __forceinline__ void store_line(const uint4& v, uint32_t sK, int row, const Geo& geo,
                                            const uint32_t (&mul_row)[Cfg<FMT, DQK>::MUL_PER_ROW + 2]) {
   using S = Stage<FMT, DQK>;
   using C = Cfg<FMT, DQK>;
+  const int piece = S::copied_line(LINE) ? geo.piece_cp : geo.piece;
   const int x = row & 7;
   const uint32_t rbase = sK + row * 128;
   const int ci = 8 * LINE + piece;
@@ -332,11 +377,22 @@ __device__ __forceinline__ void store_line(const uint4& v, uint32_t sK, int row,
 
 template <int FMT, int DQK, int LINE>
 __device__ __forceinline__ void store_lines(const uint4 (&d)[Stage<FMT, DQK>::LINES], uint32_t sK,
-                                            int row, int piece,
+                                            int row, const Geo& geo,
                                             const uint32_t (&mul_row)[Cfg<FMT, DQK>::MUL_PER_ROW + 2]) {
   if constexpr (LINE < Stage<FMT, DQK>::LINES) {
-    store_line<FMT, DQK, LINE>(d[LINE], sK, row, piece, mul_row);
-    store_lines<FMT, DQK, LINE + 1>(d, sK, row, piece, mul_row);
+    store_line<FMT, DQK, LINE>(d[LINE], sK, row, geo, mul_row);
+    store_lines<FMT, DQK, LINE + 1>(d, sK, row, geo, mul_row);
+  }
+}
+
+// The same for one line whose number is known only at run time (warp-uniform).
+template <int FMT, int DQK, int LINE = 0>
+__device__ __forceinline__ void store_one_line(const uint4& d, int line, uint32_t sK, int row,
+                                               const Geo& geo,
+                                               const uint32_t (&mul_row)[Cfg<FMT, DQK>::MUL_PER_ROW + 2]) {
+  if constexpr (LINE < Stage<FMT, DQK>::LINES) {
+    if (line == LINE) store_line<FMT, DQK, LINE>(d, sK, row, geo, mul_row);
+    else store_one_line<FMT, DQK, LINE + 1>(d, line, sK, row, geo, mul_row);
   }
 }
 
@@ -358,7 +414,9 @@ sm100_attn_kernel(const AttnParams p) {
   uint32_t* mul_tab = reinterpret_cast<uint32_t*>(sm + C::K_BYTES + C::Q_BYTES + C::P_BYTES + sizeof(Ctrl));
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  grid_dependency_wait();          // inputs may come from the kernel before this one in the stream
   if (tid == 0) stamp(p, 0);
+  if (tid == 0) stamp_cta(p, 0);
   const int req = blockIdx.x, hb = blockIdx.y, split = blockIdx.z;
   const int head0 = hb * HEADS;
   const int heads_here = min(HEADS, p.h_q - head0);
@@ -408,7 +466,8 @@ sm100_attn_kernel(const AttnParams p) {
 
   // The first tile's gather goes in flight before anything else.
   S stage;
-  const Geo geo{warp >> 2, 4 * (warp & 3) + (lane >> 3), lane & 7};
+  const Geo geo{warp >> 2, 4 * (warp & 3) + (lane & 1) + 2 * (lane >> 4),
+                ((lane >> 1) & 3) + 4 * ((lane >> 3) & 1), 2 * ((lane >> 1) & 3) + ((lane >> 3) & 1)};
   int tidx[2];       // list entries of this lane's staged rows (k-steps jsub and 4 + jsub)
   tidx[0] = list_index<EXTRA>(lv, lv.begin + geo.row(0));
   tidx[1] = list_index<EXTRA>(lv, lv.begin + geo.row(1));
@@ -419,15 +478,27 @@ sm100_attn_kernel(const AttnParams p) {
   int ridx = list_index<EXTRA>(lv, lv.begin + row);
 #pragma unroll
   for (int hh = 0; hh < S::HALVES; ++hh)
-    load_half<FMT, DQK, EXTRA>(stage.d[hh], p, lv, lv.begin + geo.row(hh), tidx[hh], geo.piece);
+    load_half<FMT, DQK, EXTRA>(stage.d[hh], p, lv, lv.begin + geo.row(hh), tidx[hh], geo);
   // List entries are fetched ahead so that no address ever waits on them: tidx / ridx
   // belong to the tile staged in registers, tidx_next / ridx_n1 to the one after,
   // ridx_n2 to the one after that.
   int tidx_next[2] = {-1, -1}, ridx_n1 = -1, ridx_n2 = -1;
+  // The warp that issues the MMAs is blocked for the length of every product, so after the
+  // first tile it stages nothing: the lines of its two row groups (k-steps 3 and 7) are
+  // spread over warps 0 .. 2 LINES - 1, one line each, held in one more register set `xd`
+  // (loaded a tile ahead like the others; xidx_next is the list entry it is loaded from).
+  constexpr bool SPARE_ISSUER = S::HALVES == 2;
+  const bool has_x = SPARE_ISSUER && warp < 2 * S::LINES;
+  const int xline = warp % S::LINES;
+  const int xk = warp < S::LINES ? ISSUE_WARP >> 2 : 4 + (ISSUE_WARP >> 2);
+  const int xrow = 16 * xk + 4 * (ISSUE_WARP & 3) + (lane & 1) + 2 * (lane >> 4);
+  int xidx_next = -1;
+  uint4 xd = make_uint4(0, 0, 0, 0);
   if (n_tiles > 1) {
     tidx_next[0] = list_index<EXTRA>(lv, lv.begin + TILE + geo.row(0));
     tidx_next[1] = list_index<EXTRA>(lv, lv.begin + TILE + geo.row(1));
     ridx_n1 = ridx_n2 = list_index<EXTRA>(lv, lv.begin + TILE + row);
+    if (has_x) xidx_next = list_index<EXTRA>(lv, lv.begin + TILE + xrow);
   }
   // Multipliers of tile row `tid` into the table of tile `slot` (threads 0..127): one
   // load of the row's scale bytes, then a packed factor per byte (0 marks the rare bytes).
@@ -507,6 +578,7 @@ sm100_attn_kernel(const AttnParams p) {
   tc_fence_after_sync();
   const uint32_t tmem = ctrl.tmem;
   if (tid == 0) stamp(p, 1);
+  if (tid == 0) stamp_cta(p, 1);
 #define TSTAMP(t, k) do { if ((t) < PROF_MAX_TILES) stamp(p, PROF_TILE0 + (t) * PROF_PER_TILE + (k)); } while (0)
 
   const uint32_t bar_k_full = smem_u32(&ctrl.k_full), bar_s_full = smem_u32(&ctrl.s_full);
@@ -558,16 +630,17 @@ sm100_attn_kernel(const AttnParams p) {
   // next tile (list entries tidx_next; `has_next` false on the last tile), so the gather
   // is spread over the whole P.V phase instead of hitting memory in one burst.
   auto refill = [&](int j0, int wait_tile, int slot, bool has_next, bool& ok) {
-#pragma unroll
-    for (int jhalf = 0; jhalf < 2; ++jhalf) {
-      const int hh = S::HALVES == 2 ? jhalf : 0;
-      const int j = 4 * jhalf + geo.jsub, trow = geo.row(jhalf);
-      if (wait_tile >= 0 && ok && !mbar_wait_warp(bar_kv_free0 + 8 * j, wait_tile & 1, lane)) {
+    const bool first = wait_tile < 0;
+    const bool spared = SPARE_ISSUER && warp == ISSUE_WARP;     // stages the first tile only
+    const bool extra = has_x && !first;
+    auto wait_free = [&](int j) {
+      if (!first && ok && !mbar_wait_warp(bar_kv_free0 + 8 * j, wait_tile & 1, lane)) {
         atomicExch(&g_attn_error, ERR_KVFREE);
         ok = false;
       }
-      uint32_t mrow[C::MUL_PER_ROW + 2];          // the row's multipliers, one vector load each 4
-      if constexpr (C::PAGED) {
+    };
+    auto row_multipliers = [&](uint32_t (&mrow)[C::MUL_PER_ROW + 2], int trow) {
+      if constexpr (C::PAGED) {                   // one vector load each 4
         const uint4* src = reinterpret_cast<const uint4*>(mul_tab + (slot * TILE + trow) * C::MUL_PER_ROW);
 #pragma unroll
         for (int k = 0; k < C::MUL_PER_ROW / 4; ++k) {
@@ -576,28 +649,61 @@ sm100_attn_kernel(const AttnParams p) {
         }
       }
       mrow[C::MUL_PER_ROW] = mrow[C::MUL_PER_ROW + 1] = 0;
-      store_lines<FMT, DQK, 0>(stage.d[hh], sK, trow, geo.piece, mrow);
-      if (jhalf == 1) {                    // tile complete: publish before reloading
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_k_full);
+    };
+    auto store_set = [&](const uint4 (&d)[S::LINES], int trow) {
+      uint32_t mrow[C::MUL_PER_ROW + 2];
+      row_multipliers(mrow, trow);
+      store_lines<FMT, DQK, 0>(d, sK, trow, geo, mrow);
+    };
+    auto publish = [&]() {                   // this warp's part of the tile is in shared memory
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_k_full);
+    };
+    if (spared && !first) {
+      publish();
+      return;
+    }
+    const bool reload = has_next && !spared;
+    if constexpr (S::HALVES == 2) {
+      // Both k-steps are staged.  The first register set is reloaded as soon as it has been
+      // stored, the second once this warp's part of the tile is published: that spreads the
+      // gather over the P.V phase (all SMs gather in step, and a burst holds the issuing
+      // warps up for as long as HBM takes to serve it) and keeps it out of the way of k_full.
+#pragma unroll
+      for (int jhalf = 0; jhalf < 2; ++jhalf) {
+        wait_free(4 * jhalf + geo.jsub);
+        if (lane == 0 && wait_tile == 2) stamp(p, 150 + 32 * jhalf + warp);       // k-step free
+        store_set(stage.d[jhalf], geo.row(jhalf));
+        if (reload && jhalf == 0)          // the same rows of the next tile
+          load_half<FMT, DQK, EXTRA>(stage.d[0], p, lv, j0 + TILE + geo.row(0), tidx_next[0], geo);
       }
-      if constexpr (S::HALVES == 2) {      // both k-steps staged: reload this one for the next tile
-        // The MMA-issuing warp starts its refill late (issuing blocks until the product is
-        // nearly done); it stores both k-steps first so as not to hold up k_full, and
-        // reloads afterwards.
-        const bool defer = warp == ISSUE_TID / 32;
-        if (has_next && !defer)
-          load_half<FMT, DQK, EXTRA>(stage.d[hh], p, lv, j0 + TILE + trow, tidx_next[jhalf], geo.piece);
-        if (has_next && defer && jhalf == 1) {
-          load_half<FMT, DQK, EXTRA>(stage.d[0], p, lv, j0 + TILE + geo.row(0), tidx_next[0], geo.piece);
-          load_half<FMT, DQK, EXTRA>(stage.d[1], p, lv, j0 + TILE + geo.row(1), tidx_next[1], geo.piece);
+      if (extra) {                         // this warp's line of the issuing warp's rows
+        wait_free(xk);
+        uint32_t mrow[C::MUL_PER_ROW + 2];
+        row_multipliers(mrow, xrow);
+        store_one_line<FMT, DQK>(xd, xline, sK, xrow, geo, mrow);
+      }
+      publish();
+      if (lane == 0 && wait_tile == 2) stamp(p, 214 + warp);                     // arrived
+      if (reload)
+        load_half<FMT, DQK, EXTRA>(stage.d[1], p, lv, j0 + TILE + geo.row(1), tidx_next[1], geo);
+      if (has_x && has_next)
+        load_one_line<FMT, DQK, EXTRA>(xd, xline, p, lv, j0 + TILE + xrow, xidx_next, geo);
+    } else {
+      // One register set: the second k-step is loaded once the first is stored, then the
+      // first k-step of the next tile.
+#pragma unroll
+      for (int jhalf = 0; jhalf < 2; ++jhalf) {
+        wait_free(4 * jhalf + geo.jsub);
+        store_set(stage.d[0], geo.row(jhalf));
+        if (jhalf == 0) {
+          load_half<FMT, DQK, EXTRA>(stage.d[0], p, lv, j0 + geo.row(1), tidx[1], geo);
+        } else {
+          publish();
+          if (has_next)
+            load_half<FMT, DQK, EXTRA>(stage.d[0], p, lv, j0 + TILE + geo.row(0), tidx_next[0], geo);
         }
-      } else {                             // one register set: second k-step now, then the next tile
-        if (jhalf == 0)
-          load_half<FMT, DQK, EXTRA>(stage.d[0], p, lv, j0 + geo.row(1), tidx[1], geo.piece);
-        else if (has_next)
-          load_half<FMT, DQK, EXTRA>(stage.d[0], p, lv, j0 + TILE + geo.row(0), tidx_next[0], geo.piece);
       }
     }
   };
@@ -622,6 +728,7 @@ sm100_attn_kernel(const AttnParams p) {
       tidx_next[0] = list_index<EXTRA>(lv, j2 + geo.row(0));
       tidx_next[1] = list_index<EXTRA>(lv, j2 + geo.row(1));
       ridx_n2 = list_index<EXTRA>(lv, j2 + row);
+      if (has_x) xidx_next = list_index<EXTRA>(lv, j2 + xrow);
     }
     // Is this thread's row masked (beyond the range, or an invalid entry under masking rules)?
     bool masked = true;
@@ -736,6 +843,7 @@ sm100_attn_kernel(const AttnParams p) {
       refill(lv.begin + (t + 1) * TILE, t, (t + 1) & 1, t + 2 < n_tiles, ok);
       if (tid == 0) TSTAMP(t + 1, 0);
       if (tid == THREADS - 32) TSTAMP(t + 1, 7);
+      if (lane == 0 && t == 2) stamp(p, 230 + warp);                             // refill returned
     }
     // The registers now hold (or are receiving) tile t + 2: publish its multipliers (read
     // after the two CTA barriers of the next iteration).
@@ -748,10 +856,15 @@ sm100_attn_kernel(const AttnParams p) {
     }
   }
 
+  // The kernel after this one in the stream (the split combine, or the next layer) may be
+  // set up on the SMs while the epilogue runs; it waits for this grid's end before it reads.
+  grid_launch_dependents();
+
   // ---- final denominators and output factors ---------------------------------------
   if (ok && !mbar_wait_warp(bar_o_done, 0, lane)) { atomicExch(&g_attn_error, ERR_ODONE); ok = false; }
   tc_fence_after_sync();
   if (tid == 0) stamp(p, 3);
+  if (tid == 0) stamp_cta(p, 2);
   if (!ok) ctrl.fail = 1;
   {
     float v[16];
@@ -811,6 +924,7 @@ sm100_attn_kernel(const AttnParams p) {
   tc_fence_before_sync();
   __syncthreads();
   if (tid == 0) stamp(p, 5);
+  if (tid == 0) stamp_cta(p, 3);
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
 }
 
@@ -829,9 +943,15 @@ cudaError_t launch_one(const AttnParams& p, cudaStream_t st) {
     configured = true;
     configured_dev = dev;
   }
-  dim3 grid(p.n_req, (p.h_q + HEADS - 1) / HEADS, p.n_splits);
-  sm100_attn_kernel<FMT, DQK, EXTRA><<<grid, THREADS, smem, st>>>(p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.n_req, (p.h_q + HEADS - 1) / HEADS, p.n_splits);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  cfg.attrs = attr;
+  cfg.numAttrs = add_overlap_attribute(attr);
+  return cudaLaunchKernelEx(&cfg, sm100_attn_kernel<FMT, DQK, EXTRA>, p);
 }
 
 }  // namespace

@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libdsv4_b200.so")
+# DSV4_B200_LIB names another build of the same library (e.g. one compiled with debug defines).
+LIB_PATH = os.environ.get("DSV4_B200_LIB") or os.path.join(_HERE, "libdsv4_b200.so")
 
 KV_BF16, KV_MODEL1, KV_V32 = 0, 1, 2
 FLAG_MASK_INVALID, FLAG_IMPL_SIMPLE, FLAG_NO_COMBINE = 1, 2, 4
