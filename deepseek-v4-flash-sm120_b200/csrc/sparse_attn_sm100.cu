@@ -124,6 +124,12 @@ __device__ __forceinline__ uint4 ldg16(const uint8_t* p) {
   return v;
 }
 
+__device__ __forceinline__ uint32_t ldg_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+
 // Column-wise reduction, over the 32 lanes of a warp, of a 16-column slice held
 // one row per lane: afterwards v[0] of lane l is the reduction of column l & 15.
 template <bool IS_MAX>
@@ -464,7 +470,9 @@ sm100_attn_kernel(const AttnParams p) {
     return;
   }
 
-  // The first tile's gather goes in flight before anything else.
+  // Set-up.  Order matters for latency: the list entries are requested first, then Q (which
+  // depends on nothing), then, as the entries arrive, the first tile's rows and their scale
+  // bytes; Q and the multipliers are written to shared memory while the rows are in flight.
   S stage;
   const Geo geo{warp >> 2, 4 * (warp & 3) + (lane & 1) + 2 * (lane >> 4),
                 ((lane >> 1) & 3) + 4 * ((lane >> 3) & 1), 2 * ((lane >> 1) & 3) + ((lane >> 3) & 1)};
@@ -476,9 +484,6 @@ sm100_attn_kernel(const AttnParams p) {
   const int row = lg * 32 + lane;
   // The list entry of this thread's own tile row (masking; scale-table fill by tid < 128).
   int ridx = list_index<EXTRA>(lv, lv.begin + row);
-#pragma unroll
-  for (int hh = 0; hh < S::HALVES; ++hh)
-    load_half<FMT, DQK, EXTRA>(stage.d[hh], p, lv, lv.begin + geo.row(hh), tidx[hh], geo);
   // List entries are fetched ahead so that no address ever waits on them: tidx / ridx
   // belong to the tile staged in registers, tidx_next / ridx_n1 to the one after,
   // ridx_n2 to the one after that.
@@ -500,31 +505,58 @@ sm100_attn_kernel(const AttnParams p) {
     ridx_n1 = ridx_n2 = list_index<EXTRA>(lv, lv.begin + TILE + row);
     if (has_x) xidx_next = list_index<EXTRA>(lv, lv.begin + TILE + xrow);
   }
-  // Multipliers of tile row `tid` into the table of tile `slot` (threads 0..127): one
-  // load of the row's scale bytes, then a packed factor per byte (0 marks the rare bytes).
-  auto fill_scales = [&](int slot, int j, int idx) {
+  // Multipliers of tile row `tid` into the table of tile `slot` (threads 0..127): one load
+  // of the row's scale bytes (issued early, `ScaleWords`), later a pair of packed factors
+  // per byte into the table.
+  struct ScaleWords { uint32_t w[C::PAGED ? KvTraits<C::PAGED ? FMT : DSV4_KV_V32>::SLOTS / 4 : 1]; };
+  auto load_scales = [&](int j, int idx) {
+    ScaleWords sw;
     if constexpr (C::PAGED) {
       using T = KvTraits<FMT>;
+#pragma unroll
+      for (int k = 0; k < T::SLOTS / 4; ++k) sw.w[k] = 0x7f7f7f7fu;
       if (tid < TILE) {
         const uint8_t* scl;
         const uint8_t* r = row_ptr<FMT>(cache_of<EXTRA>(p, lv, j), j < lv.end ? idx : -1, scl);
-        uint32_t w[T::SLOTS / 4];
+        if (r != nullptr) {
 #pragma unroll
-        for (int k = 0; k < T::SLOTS / 4; ++k)
-          w[k] = r != nullptr ? __ldg(reinterpret_cast<const uint32_t*>(scl) + k) : 0x7f7f7f7fu;
+          for (int k = 0; k < T::SLOTS / 4; ++k) sw.w[k] = ldg_u32(reinterpret_cast<const uint32_t*>(scl) + k);
+        }
+      }
+    } else {
+      sw.w[0] = 0;
+    }
+    return sw;
+  };
+  auto store_scales = [&](int slot, const ScaleWords& sw) {
+    if constexpr (C::PAGED) {
+      using T = KvTraits<FMT>;
+      if (tid < TILE) {
         uint32_t* dst = mul_tab + (slot * TILE + tid) * C::MUL_PER_ROW;
 #pragma unroll
         for (int k = 0; k < T::N_SCALE; ++k) {
-          const ScaleMul m = make_scale_mul((w[k >> 2] >> (8 * (k & 3))) & 0xffu);
+          const ScaleMul m = make_scale_mul((sw.w[k >> 2] >> (8 * (k & 3))) & 0xffu);
           dst[2 * k] = m.c1;
           dst[2 * k + 1] = m.c2;
         }
       }
     }
   };
-  fill_scales(0, lv.begin + row, ridx);
 
-  // ---- set-up: barriers, TMEM, Q ---------------------------------------------------
+  // ---- set-up: Q requests, barriers, TMEM, first tile -----------------------------------
+  // Q[head][d] -> blocks [d/64][head][64], 128-byte swizzle; absent heads are zero.
+  const __nv_bfloat16* qrow0 = p.q + bi * p.stride_q_b + si * p.stride_q_s + head0 * p.stride_q_h;
+  constexpr int Q_CHUNKS = HEADS * C::NB * 8;
+  constexpr int Q_BATCH = (Q_CHUNKS + THREADS - 1) / THREADS;     // all in flight at once
+  uint4 qv[Q_BATCH];
+#pragma unroll
+  for (int it = 0; it < Q_BATCH; ++it) {
+    const int i = tid + it * THREADS;
+    const int h = i / (C::NB * 8), cc = i % (C::NB * 8);
+    qv[it] = make_uint4(0, 0, 0, 0);
+    if (i < Q_CHUNKS && h < heads_here)
+      qv[it] = ldg16(reinterpret_cast<const uint8_t*>(qrow0 + h * p.stride_q_h) + 16 * cc);
+  }
   if (tid == 0) {
     mbar_init(smem_u32(&ctrl.k_full), WARPS);
     mbar_init(smem_u32(&ctrl.s_full), 1);
@@ -544,34 +576,20 @@ sm100_attn_kernel(const AttnParams p) {
     tmem_alloc(smem_u32(&ctrl.tmem), TMEM_COLS);
     tmem_relinquish();
   }
-  {
-    // Q[head][d] -> blocks [d/64][head][64], 128-byte swizzle; absent heads are zero.
-    // All of a thread's loads are issued before its first store so their latencies overlap.
-    const __nv_bfloat16* qrow0 = p.q + bi * p.stride_q_b + si * p.stride_q_s + head0 * p.stride_q_h;
-    constexpr int Q_CHUNKS = HEADS * C::NB * 8;
-    constexpr int Q_BATCH = (HEADS * C::NB * 8 + THREADS - 1) / THREADS;   // all in flight at once
-    constexpr int Q_ITERS = (Q_CHUNKS + THREADS * Q_BATCH - 1) / (THREADS * Q_BATCH);
-#pragma unroll 1
-    for (int ob = 0; ob < Q_ITERS; ++ob) {
-      uint4 qv[Q_BATCH];
+  // First use of the list entries: the first tile's rows and scale bytes go in flight.
 #pragma unroll
-      for (int it = 0; it < Q_BATCH; ++it) {
-        const int i = tid + (ob * Q_BATCH + it) * THREADS;
-        const int h = i / (C::NB * 8), cc = i % (C::NB * 8);
-        qv[it] = make_uint4(0, 0, 0, 0);
-        if (i < Q_CHUNKS && h < heads_here)
-          qv[it] = __ldg(reinterpret_cast<const uint4*>(qrow0 + h * p.stride_q_h) + cc);
-      }
+  for (int hh = 0; hh < S::HALVES; ++hh)
+    load_half<FMT, DQK, EXTRA>(stage.d[hh], p, lv, lv.begin + geo.row(hh), tidx[hh], geo);
+  const ScaleWords sw0 = load_scales(lv.begin + row, ridx);
 #pragma unroll
-      for (int it = 0; it < Q_BATCH; ++it) {
-        const int i = tid + (ob * Q_BATCH + it) * THREADS;
-        const int h = i / (C::NB * 8), cc = i % (C::NB * 8), kb = cc >> 3, ch = cc & 7;
-        if (i < Q_CHUNKS)
-          st_shared_v4(sQ + kb * QBLOCK_BYTES + h * 128 + ((ch ^ (h & 7)) << 4), qv[it].x, qv[it].y,
-                       qv[it].z, qv[it].w);
-      }
-    }
+  for (int it = 0; it < Q_BATCH; ++it) {
+    const int i = tid + it * THREADS;
+    const int h = i / (C::NB * 8), cc = i % (C::NB * 8), kb = cc >> 3, ch = cc & 7;
+    if (i < Q_CHUNKS)
+      st_shared_v4(sQ + kb * QBLOCK_BYTES + h * 128 + ((ch ^ (h & 7)) << 4), qv[it].x, qv[it].y,
+                   qv[it].z, qv[it].w);
   }
+  store_scales(0, sw0);
   fence_async_smem();
   tc_fence_before_sync();
   __syncthreads();
@@ -715,6 +733,7 @@ sm100_attn_kernel(const AttnParams p) {
   for (int i = 0; i < COLS_PER_WARP; ++i) lsum[i] = 0.f;
 
 
+  ScaleWords sw_next = {};
   // Iteration t = -1 only fills the first tile; iteration t >= 0 runs tile t and, behind
   // its P.V product, fills tile t + 1.
 #pragma unroll 1
@@ -742,6 +761,9 @@ sm100_attn_kernel(const AttnParams p) {
 
     if (ok && !mbar_wait_warp(bar_s_full, t & 1, lane)) { atomicExch(&g_attn_error, ERR_SFULL); ok = false; }
     tc_fence_after_sync();
+    // Scale bytes of the tile after next (its list entries arrived during Q.K^T); they
+    // become multipliers at the end of this iteration.
+    if (t + 2 < n_tiles) sw_next = load_scales(lv.begin + (t + 2) * TILE + row, ridx_n2);
     if (tid == 0) TSTAMP(t, 2);
 
     // pass 1: per-head max over the tile's rows
@@ -849,7 +871,8 @@ sm100_attn_kernel(const AttnParams p) {
     // after the two CTA barriers of the next iteration).
     tidx[0] = tidx_next[0];
     tidx[1] = tidx_next[1];
-    if (t + 2 < n_tiles) fill_scales(t & 1, lv.begin + (t + 2) * TILE + row, ridx_n2);
+    if (t >= 0 && t + 2 < n_tiles) store_scales(t & 1, sw_next);
+    if (t < 0 && n_tiles > 1) store_scales(1, load_scales(lv.begin + TILE + row, ridx_n2));
     if (t >= 0) {
       ridx = ridx_n1;
       ridx_n1 = ridx_n2;
