@@ -46,6 +46,11 @@ N_INDEX_SETS = 16
 METRIC = "sparse_decode_achieved_hbm_bandwidth"
 
 
+# DRAM bytes per launch of the decode kernel from the committed ncu capture (bytes; the
+# capture is of this very workload, so nothing is scaled).
+NCU_DRAM_BYTES_PER_LAUNCH = {"cfg2": 24.21e6 + 0.03e6}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -407,7 +412,11 @@ def run_ours(args):
                        "l2_policy": f"rotates {N_INDEX_SETS} index sets (~{N_INDEX_SETS * wl.kv_gather_bytes() / 1e6:.0f} MB of distinct rows) so inputs exceed L2",
                        "parallelism": f"request-parallel x{world}, no collective"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "frac": achieved / peak,
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload),
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per launch, "
+                                           "profiles/sm100_attn_kernel_decode_cfg2.md",
+                         "peak_source": peak_src,
                          "kernel": "sparse decode (gather+dequant+QK^T+softmax+PV)",
                          "kernel_us": k_ms * 1e3, "algorithmic_bytes_per_launch": mean_bytes,
                          "kv_gather_gbs": wl.kv_gather_bytes() / (k_ms * 1e-3) / 1e9,
