@@ -24,6 +24,7 @@ struct AttnParams {
   int n_req;          // decode: b * s_q ; prefill: s_q
   int s_q;            // decode: query tokens per request ; prefill: 1
   int h_q, topk, extra_topk, n_splits, flags, mode;
+  int cluster;        // splits merged on chip per thread-block cluster (1, 2 or 4; divides n_splits)
   int page_block, n_tok;              // main cache: tokens per page, total tokens (s_kv)
   int extra_page_block, extra_n_tok;
   int page_shift, extra_page_shift;   // log2 of the page size, or -1 when it is not a power of two

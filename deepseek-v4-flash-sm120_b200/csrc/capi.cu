@@ -149,6 +149,33 @@ int dsv4_split_combine(const Dsv4CombineArgs* a, void* stream) {
   return e ? cuda_fail(e) : DSV4_OK;
 }
 
+// Splits merged on chip by one thread-block cluster of the tensor-core kernel.  The merge
+// pays when it makes the output final (no partials through L2, no combine launch): measured
+// on B200, two splits per request (b = 64) gain 8 % per call, whereas merging 8 splits in
+// groups of 2 or 4 and still combining the groups loses 9-11 %.  So: the whole request in one
+// cluster when n_splits is 2 or 4 (clusters of 4 CTAs with this kernel's shared-memory
+// footprint still fill the GPU, clusters of 8 do not), otherwise no cluster.
+// DSV4_CLUSTER=1 turns clusters off; DSV4_CLUSTER=group forces groups of 2 or 4 for any
+// n_splits they divide (measurement hook).
+static int cluster_size_for(int n_splits, bool simple_impl) {
+  if (simple_impl || n_splits < 2) return 1;
+  static const int mode = [] {
+    const char* e = std::getenv("DSV4_CLUSTER");
+    if (!e) return 0;
+    if (!std::strcmp(e, "group")) return 2;
+    return std::atoi(e) == 1 ? 1 : 0;
+  }();
+  if (mode == 1) return 1;
+  if (mode == 2) return (n_splits % 4 == 0) ? 4 : (n_splits % 2 == 0) ? 2 : 1;
+  return (n_splits == 2 || n_splits == 4) ? n_splits : 1;
+}
+
+int dsv4_decode_partial_sets(const Dsv4DecodeArgs* a) {
+  if (!a || a->n_splits < 1) return 0;
+  const bool simple = want_simple(a->flags) || !dsv4::sm100_attn_supported(a->kv_format, a->d_qk);
+  return a->n_splits / cluster_size_for(a->n_splits, simple);
+}
+
 int dsv4_sparse_decode(const Dsv4DecodeArgs* a, void* stream) {
   if (!a || !a->q || !a->kv || !a->indices || !a->out || !a->lse) return DSV4_ERR_NULL;
   if (a->b < 0 || a->s_q < 1 || a->h_q < 1 || a->topk < 1 || a->num_blocks < 1 ||
@@ -178,6 +205,9 @@ int dsv4_sparse_decode(const Dsv4DecodeArgs* a, void* stream) {
   p.topk = a->topk;
   p.extra_topk = a->extra_kv ? a->extra_topk : 0;
   p.n_splits = a->n_splits;
+  const bool simple = want_simple(a->flags) || !dsv4::sm100_attn_supported(a->kv_format, a->d_qk);
+  p.cluster = cluster_size_for(a->n_splits, simple);
+  const int partial_sets = a->n_splits / p.cluster;
   p.flags = a->flags;
   p.mode = dsv4::MODE_DECODE;
   p.page_block = a->page_block_size;
@@ -210,14 +240,14 @@ int dsv4_sparse_decode(const Dsv4DecodeArgs* a, void* stream) {
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
-  if (want_simple(a->flags) || !dsv4::sm100_attn_supported(a->kv_format, a->d_qk))
+  if (simple)
     e = dsv4::launch_simple_attn(p, a->kv_format, a->d_qk, st);
   else
     e = dsv4::launch_sm100_attn(p, a->kv_format, a->d_qk, st);
   if (e) return cuda_fail(e);
-  if (a->n_splits > 1 && !(a->flags & DSV4_FLAG_NO_COMBINE)) {
+  if (partial_sets > 1 && !(a->flags & DSV4_FLAG_NO_COMBINE)) {
     Dsv4CombineArgs c{};
-    c.n_rows = p.n_req; c.s_q = a->s_q; c.h_q = a->h_q; c.n_splits = a->n_splits;
+    c.n_rows = p.n_req; c.s_q = a->s_q; c.h_q = a->h_q; c.n_splits = partial_sets;
     c.o_accum = a->o_accum; c.lse_accum = a->lse_accum; c.attn_sink = a->attn_sink;
     c.out = a->out; c.lse = a->lse;
     c.stride_o_b = a->stride_o_b; c.stride_o_s = a->stride_o_s; c.stride_o_h = a->stride_o_h;
@@ -253,6 +283,7 @@ int dsv4_sparse_prefill(const Dsv4PrefillArgs* a, void* stream) {
   p.h_q = a->h_q;
   p.topk = a->topk;
   p.n_splits = 1;
+  p.cluster = 1;
   p.flags = a->flags;
   p.mode = dsv4::MODE_PREFILL;
   p.page_block = a->kv_format == DSV4_KV_BF16 ? 1 : a->page_block_size;

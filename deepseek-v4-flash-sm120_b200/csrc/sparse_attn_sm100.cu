@@ -85,11 +85,13 @@ struct Ctrl {
   uint32_t tmem;
   int resc[2];
   int fail;
-  float wred[4][HEADS];                // per-lane-group column partials (max, then sums)
-  float mref[HEADS];                   // reference max, log2-scaled units
+  alignas(16) float wred[4][HEADS];    // per-lane-group column partials (max, then sums)
+  alignas(16) float mref[HEADS];       // reference max, log2-scaled units (read as float4)
   float mtrue[HEADS];                  // true running max, log2-scaled units
   float alpha[HEADS];                  // rescale factor / final output factor
 };
+
+static_assert(sizeof(Ctrl) % 16 == 0, "the multiplier table behind Ctrl is read as uint4");
 
 template <int FMT, int DQK>
 constexpr size_t smem_bytes() {
@@ -403,6 +405,162 @@ __device__ __forceinline__ void store_one_line(const uint4& d, int line, uint32_
 }
 
 // ---------------------------------------------------------------------------
+// Merging the splits of one request inside a thread-block cluster.
+// The `cs` CTAs of a cluster (consecutive splits, cluster dimension z) finish with
+// un-normalised O^T in TMEM, denominators l[h] and reference maxima m[h].  They
+//   1. publish (l, m) in their own shared memory and meet at a cluster barrier, after
+//      which every CTA's K tile region is free (its last product has completed);
+//   2. read all (l, m) through distributed shared memory and scale their own O^T by
+//      2^(m_own - M) / L (times the sink factor when this cluster holds all splits);
+//   3. push slice r of the scaled O^T (d in [r, r+1) * 512 / cs) into CTA r's staging
+//      area [source][head][d_local] (fp32, 128 KB) with st.shared::cluster;
+//   4. meet again; each CTA sums its slice over the sources in rank order and writes
+//      either the final BF16 output or one normalised partial per cluster.
+// Partial traffic to L2 and the combine kernel's input shrink by the cluster size, and
+// with n_splits == cs there is no combine launch at all.  An empty split (no tile) takes
+// part with l = 0, m = -inf and a slice of zeros; a CTA whose bounded wait gave up still
+// walks every barrier (its peers must not be left waiting) and only drops its own stores.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
+// Everything the merge needs, by value (the kernel's parameter block must not have its
+// address taken: that would move it to local memory for the whole kernel).
+struct MergeOut {
+  int cluster, n_splits, mode;
+  const float* sink;
+  float* lse;
+  float* lse_accum;
+  float* o_accum;
+  __nv_bfloat16* out;
+  int64_t stride_o_b, stride_o_s, stride_o_h, stride_lse_b, stride_lse_s, stride_lse_h;
+};
+__device__ __forceinline__ MergeOut merge_out_of(const AttnParams& p) {
+  return MergeOut{p.cluster, p.n_splits, p.mode, p.sink, p.lse, p.lse_accum, p.o_accum, p.out,
+                  p.stride_o_b, p.stride_o_s, p.stride_o_h, p.stride_lse_b, p.stride_lse_s,
+                  p.stride_lse_h};
+}
+struct MergeCtx {
+  uint32_t stage;          // shared address of the staging area (the K tile region)
+  uint32_t tmem_o;         // TMEM address of this warp's lanes of O^T (column COL_O), or unused
+  int heads_here, head0, bi, si;
+  int64_t acc_slot0;       // (cluster index * n_req + req) * h_q + head0
+  bool empty;              // this split had no tile: no TMEM, contributes zeros
+};
+
+__device__ __noinline__ void cluster_merge(const MergeOut p, Ctrl& ctrl, const MergeCtx c,
+                                           float l_own, float m_own) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int cs = p.cluster;
+  const uint32_t rank = cluster_rank();
+  const bool final_out = p.n_splits == cs;
+  const int dl = D_V / cs;                               // slice width per rank
+
+  if (tid < HEADS) {
+    ctrl.wred[0][tid] = l_own;
+    ctrl.wred[1][tid] = m_own;
+  }
+  cluster_sync_all();                                    // (1) everyone's K tile is free too
+
+  if (tid < HEADS) {
+    const uint32_t a_l = smem_u32(&ctrl.wred[0][tid]), a_m = smem_u32(&ctrl.wred[1][tid]);
+    float big = -INFINITY;
+    for (int r = 0; r < cs; ++r) big = fmaxf(big, ld_cluster_f32(map_to_rank(a_m, r)));
+    float total = 0.f;
+    for (int r = 0; r < cs; ++r) {
+      const float mr = ld_cluster_f32(map_to_rank(a_m, r));
+      const float lr = ld_cluster_f32(map_to_rank(a_l, r));
+      if (mr != -INFINITY) total += ex2(mr - big) * lr;
+    }
+    const float w_own = (m_own == -INFINITY) ? 0.f : ex2(m_own - big);
+    float f;
+    if (final_out) {
+      const bool has_sink = p.sink != nullptr;
+      float lse_v, ml_v;
+      f = finalize_row(p.mode, big == -INFINITY ? -INFINITY : big * LN2, total, has_sink,
+                       (has_sink && tid < c.heads_here) ? p.sink[c.head0 + tid] : 0.f, lse_v, ml_v);
+      if (rank == 0 && tid < c.heads_here && !ctrl.fail)
+        p.lse[c.bi * p.stride_lse_b + c.si * p.stride_lse_s + (c.head0 + tid) * p.stride_lse_h] = lse_v;
+    } else {
+      const bool none = !(total > 0.f);
+      f = none ? 0.f : 1.f / total;
+      if (rank == 0 && tid < c.heads_here && !ctrl.fail)
+        p.lse_accum[c.acc_slot0 + tid] = none ? -INFINITY : logf(total) + big * LN2;
+    }
+    ctrl.alpha[tid] = w_own * f;
+  }
+  __syncthreads();
+
+  // (3) push: thread = one d (TMEM lane), 16 heads per TMEM load
+  {
+    const int m = warp >> 2, lg = warp & 3;
+    const int d = m * 128 + lg * 32 + lane;
+    const uint32_t owner = d / dl;
+    const int d_local = d - owner * dl;
+    const uint32_t dst0 = map_to_rank(c.stage + ((rank * HEADS) * dl + d_local) * 4, owner);
+#pragma unroll 1
+    for (int c4 = 0; c4 < HEADS / 16; ++c4) {
+      uint32_t o[16];
+      if (!c.empty) {
+        tmem_ld16(c.tmem_o + m * HEADS + c4 * 16, o);
+        tmem_ld_wait();
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int h = c4 * 16 + i;
+        const float val = c.empty ? 0.f : __uint_as_float(o[i]) * ctrl.alpha[h];
+        st_cluster_f32(dst0 + h * dl * 4, val);
+      }
+    }
+  }
+  cluster_sync_all();                                    // (4) all slices have landed
+
+  // sum this rank's slice over the sources, 4 consecutive d per thread
+  if (!ctrl.fail) {
+    const int quads = dl / 4;
+    __nv_bfloat16* out_base = p.out + c.bi * p.stride_o_b + c.si * p.stride_o_s + c.head0 * p.stride_o_h;
+    for (int item = tid; item < c.heads_here * quads; item += THREADS) {
+      const int h = item / quads, q = item - h * quads;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < cs; ++r) {
+        float4 v;
+        const uint32_t a = c.stage + (((r * HEADS + h) * dl) + 4 * q) * 4;
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a) : "memory");
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      const int d0 = rank * dl + 4 * q;
+      if (final_out) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+        *reinterpret_cast<uint2*>(out_base + h * p.stride_o_h + d0) =
+            make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+      } else {
+        *reinterpret_cast<float4*>(p.o_accum + (c.acc_slot0 + h) * D_V + d0) = acc;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------
 template <int FMT, int DQK, bool EXTRA>
@@ -440,9 +598,18 @@ sm100_attn_kernel(const AttnParams p) {
                             : nullptr;
   const int n_tiles = (lv.end - lv.begin + TILE - 1) / TILE;
 
-  const int64_t acc_slot0 = (static_cast<int64_t>(split) * p.n_req + req) * p.h_q + head0;
+  // Partials are indexed by cluster when the splits of a cluster are merged on chip.
+  const int64_t acc_slot0 = (static_cast<int64_t>(split / p.cluster) * p.n_req + req) * p.h_q + head0;
   __nv_bfloat16* out_base = p.out + bi * p.stride_o_b + si * p.stride_o_s + head0 * p.stride_o_h;
 
+  if (n_tiles == 0 && p.cluster > 1) {
+    // Nothing to attend to, but the peers of the cluster count on this CTA at their barriers.
+    if (tid == 0) ctrl.fail = 0;
+    __syncthreads();
+    MergeCtx mc{sK, 0u, heads_here, head0, bi, si, acc_slot0, true};
+    cluster_merge(merge_out_of(p), ctrl, mc, 0.f, -INFINITY);
+    return;
+  }
   if (n_tiles == 0) {
     // Nothing to attend to: write the empty result directly (uniform branch).
     const bool has_sink = p.sink != nullptr;
@@ -897,6 +1064,15 @@ sm100_attn_kernel(const AttnParams p) {
     if (lane < 16) ctrl.wred[lg][cg * 16 + lane] = cm;
   }
   __syncthreads();
+  if (p.cluster > 1) {
+    float l = 0.f, mr = -INFINITY;
+    if (tid < HEADS) {
+      l = ctrl.wred[0][tid] + ctrl.wred[1][tid] + ctrl.wred[2][tid] + ctrl.wred[3][tid];
+      mr = ctrl.mref[tid];
+    }
+    MergeCtx mc{sK, tmem + tlane + COL_O, heads_here, head0, bi, si, acc_slot0, false};
+    cluster_merge(merge_out_of(p), ctrl, mc, l, mr);
+  } else {
   if (tid < HEADS && !ctrl.fail) {
     const float l = ctrl.wred[0][tid] + ctrl.wred[1][tid] + ctrl.wred[2][tid] + ctrl.wred[3][tid];
     const float mr = ctrl.mref[tid];
@@ -941,6 +1117,7 @@ sm100_attn_kernel(const AttnParams p) {
       }
     }
   }
+  }  // not clustered
 
   // ---- teardown --------------------------------------------------------------------
   if (tid == 0) stamp(p, 4);
@@ -971,9 +1148,16 @@ cudaError_t launch_one(const AttnParams& p, cudaStream_t st) {
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   cfg.attrs = attr;
   cfg.numAttrs = add_overlap_attribute(attr);
+  if (p.cluster > 1) {
+    attr[cfg.numAttrs].id = cudaLaunchAttributeClusterDimension;
+    attr[cfg.numAttrs].val.clusterDim.x = 1;
+    attr[cfg.numAttrs].val.clusterDim.y = 1;
+    attr[cfg.numAttrs].val.clusterDim.z = p.cluster;
+    ++cfg.numAttrs;
+  }
   return cudaLaunchKernelEx(&cfg, sm100_attn_kernel<FMT, DQK, EXTRA>, p);
 }
 

@@ -62,6 +62,7 @@ SYMBOLS = {
     "dsv4_device_info": (C.c_int, [C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int),
                                    C.POINTER(C.c_int)]),
     "dsv4_plan_splits": (C.c_int, [C.c_int] * 6),
+    "dsv4_decode_partial_sets": (C.c_int, [C.POINTER(DecodeArgs)]),
     "dsv4_sparse_decode": (C.c_int, [C.POINTER(DecodeArgs), vp]),
     "dsv4_sparse_decode_noalloc": (C.c_int, [C.POINTER(DecodeArgs), vp]),
     "dsv4_split_combine": (C.c_int, [C.POINTER(CombineArgs), vp]),

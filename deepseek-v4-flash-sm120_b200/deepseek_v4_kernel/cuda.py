@@ -352,8 +352,10 @@ class DecodeCall:
         a.stride_o_b, a.stride_o_s, a.stride_o_h = self.out.stride(0), self.out.stride(1), self.out.stride(2)
         a.stride_lse_b, a.stride_lse_h, a.stride_lse_s = self.lse.stride(0), self.lse.stride(1), self.lse.stride(2)
         self.args = a
+        # partial sets the decode kernel leaves behind (splits are merged in groups on chip)
+        self.partial_sets = N.lib.dsv4_decode_partial_sets(C.byref(a))
         c = N.CombineArgs()
-        c.n_rows, c.s_q, c.h_q, c.n_splits = b * s_q, s_q, h_q, self.n_splits
+        c.n_rows, c.s_q, c.h_q, c.n_splits = b * s_q, s_q, h_q, self.partial_sets
         c.o_accum, c.lse_accum, c.attn_sink = a.o_accum, a.lse_accum, a.attn_sink
         c.out, c.lse = a.out, a.lse
         c.stride_o_b, c.stride_o_s, c.stride_o_h = a.stride_o_b, a.stride_o_s, a.stride_o_h
@@ -370,9 +372,9 @@ class DecodeCall:
         N.check(N.lib.dsv4_sparse_decode(C.byref(self.args), stream), "dsv4_sparse_decode")
 
     def combine(self, stream: int) -> None:
-        if self.n_splits > 1:
+        if self.partial_sets > 1:
             N.check(N.lib.dsv4_split_combine(C.byref(self.cargs), stream), "dsv4_split_combine")
 
     @property
     def launches_per_call(self) -> int:
-        return 2 if self.n_splits > 1 else 1
+        return 2 if self.partial_sets > 1 else 1

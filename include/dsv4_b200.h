@@ -72,9 +72,13 @@ enum Dsv4Flags {
  * stride_extra_kv_block which are in BYTES.  All inner dimensions are dense.
  * q rows and KV pages must be 16-byte aligned.
  *
- * When n_splits > 1 each request's list is cut into n_splits ranges that write
- * locally normalised fp32 partials to o_accum [n_splits, b*s_q, h_q, 512] and
- * lse_accum [n_splits, b*s_q, h_q]; the same call then runs the combine step.
+ * When n_splits > 1 each request's list is cut into n_splits ranges.  Groups of
+ * consecutive ranges (4, 2 or 1 of them: a thread-block cluster) are merged on
+ * chip; each group writes one locally normalised fp32 partial to o_accum
+ * [n_splits, b*s_q, h_q, 512] / lse_accum [n_splits, b*s_q, h_q] (the first
+ * dsv4_decode_partial_sets(args) slots are used), and the same call then runs
+ * the combine step over those.  With a single group the result is final and
+ * neither scratch nor a combine is touched.
  * ------------------------------------------------------------------------- */
 typedef struct Dsv4DecodeArgs {
   int32_t b, s_q, h_q, d_qk, d_v, topk;
@@ -144,6 +148,12 @@ int dsv4_sparse_decode_noalloc(const Dsv4DecodeArgs* args, void* cuda_stream);
  * csrc/api/sparse_decode.cpp:147-171 (the policy differs: it is sized for one
  * CTA per SM that owns up to 64 heads and walks 128-row tiles).                  */
 int dsv4_plan_splits(int b, int s_q, int h_q, int topk, int extra_topk, int num_sms);
+
+/* Number of partial sets a decode call with these arguments leaves in o_accum /
+ * lse_accum (n_splits divided by the on-chip merge width; 1 = none, the output is
+ * final).  Callers that pass DSV4_FLAG_NO_COMBINE give this as n_splits to
+ * dsv4_split_combine.  No reference counterpart.                                  */
+int dsv4_decode_partial_sets(const Dsv4DecodeArgs* args);
 
 /* ---------------------------------------------------------------------------
  * Split-KV combine alone: replaces dsv4_split_kv_combine

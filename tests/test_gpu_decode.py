@@ -182,3 +182,50 @@ def test_plan_is_used_and_outputs_have_reference_shapes(cuda_mod):
     with pytest.raises(RuntimeError):
         cuda_mod.sparse_decode_fwd(q.cuda(), kv4.view(8, 64, 1, 584)[..., :580], idx.cuda(), None, None,
                                    None, None, None, None, None, 512, 0.044)
+
+
+@pytest.mark.parametrize("layout", [O.MODEL1, O.V32], ids=["model1", "v32"])
+@pytest.mark.parametrize("n_splits", [2, 4])
+def test_cluster_merge_with_empty_and_ragged_splits(cuda_mod, layout, n_splits):
+    """Two and four splits are merged inside one thread-block cluster (no combine
+    launch).  Lengths are chosen so that some CTAs of a cluster own no tile at all
+    (they still take part in the merge), some a ragged one; with a sink."""
+    q, pages, idx = fake_batch(5, 64, 8, 600, seed=77, layout=layout)
+    tk = torch.tensor([1, 17, 40, 333, 600], dtype=torch.int32)
+    sink = torch.randn(64, generator=torch.Generator().manual_seed(5))
+    sm = 1.0 / math.sqrt(layout.d_qk)
+    out, lse = run(cuda_mod, q, pages, idx, sm, tk, sink, 0, n_splits, layout)
+    out_ref, lse_ref = O.sparse_decode(q, pages, idx, tk, sink, sm, 64, layout)
+    check(out, lse, out_ref, lse_ref)
+
+
+def test_grouped_cluster_merge_feeds_the_combine():
+    """DSV4_CLUSTER=group merges the splits in groups of 4 and combines the groups
+    (a measurement configuration; the variable is read once per process, hence the
+    child process).  8 and 16 splits, one request shorter than a group."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import math, sys, torch
+sys.path[:0] = [%r, %r]
+from oracle import sparse_mla as O
+import test_gpu_decode as T
+from deepseek_v4_kernel import cuda as K
+q, pages, idx = T.fake_batch(3, 64, 16, 1024, seed=91, layout=O.V32)
+tk = torch.tensor([1024, 700, 30], dtype=torch.int32)
+sm = 1.0 / math.sqrt(576)
+ref = O.sparse_decode(q, pages, idx, tk, None, sm, 64, O.V32)
+for n in (8, 16):
+    out, lse = T.run(K, q, pages, idx, sm, tk, None, 0, n, O.V32)
+    T.check(out, lse, *ref)
+print("ok")
+''' % (os.path.dirname(os.path.abspath(__file__)),
+       os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                    "deepseek-v4-flash-sm120_b200"))
+    env = dict(os.environ, DSV4_CLUSTER="group")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
+    res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True,
+                         timeout=240)
+    assert res.returncode == 0 and "ok" in res.stdout, res.stdout + res.stderr
