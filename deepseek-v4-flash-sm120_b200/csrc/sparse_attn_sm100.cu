@@ -407,19 +407,22 @@ __device__ __forceinline__ void store_one_line(const uint4& d, int line, uint32_
 // ---------------------------------------------------------------------------
 // Merging the splits of one request inside a thread-block cluster.
 // The `cs` CTAs of a cluster (consecutive splits, cluster dimension z) finish with
-// un-normalised O^T in TMEM, denominators l[h] and reference maxima m[h].  They
-//   1. publish (l, m) in their own shared memory and meet at a cluster barrier, after
-//      which every CTA's K tile region is free (its last product has completed);
-//   2. read all (l, m) through distributed shared memory and scale their own O^T by
-//      2^(m_own - M) / L (times the sink factor when this cluster holds all splits);
-//   3. push slice r of the scaled O^T (d in [r, r+1) * 512 / cs) into CTA r's staging
-//      area [source][head][d_local] (fp32, 128 KB) with st.shared::cluster;
-//   4. meet again; each CTA sums its slice over the sources in rank order and writes
-//      either the final BF16 output or one normalised partial per cluster.
+// un-normalised O^T in TMEM, denominators l[h] and reference maxima m[h].  Each CTA
+//   1. copies its O^T, as it is, into its own shared memory as [head][d] fp32 (128 KB in
+//      the K tile region, which its own last product has released) and publishes (l, m);
+//   2. meets the others at a cluster barrier;
+//   3. reads every CTA's (l, m) through distributed shared memory and derives, per head,
+//      the weights 2^(m_s - M) / L of all sources (times the sink factor when this
+//      cluster holds all splits of the request);
+//   4. pulls slice r = its rank (d in [r, r+1) * 512 / cs) of every source with 16-byte
+//      ld.shared::cluster loads, sums in rank order and writes either the final BF16
+//      output or one normalised fp32 partial per cluster;
+//   5. meets the others again, so that no CTA retires while its memory is still read.
 // Partial traffic to L2 and the combine kernel's input shrink by the cluster size, and
 // with n_splits == cs there is no combine launch at all.  An empty split (no tile) takes
-// part with l = 0, m = -inf and a slice of zeros; a CTA whose bounded wait gave up still
-// walks every barrier (its peers must not be left waiting) and only drops its own stores.
+// part with l = 0, m = -inf (weight 0; its memory is not read); a CTA whose bounded wait
+// gave up still walks every barrier (its peers must not be left waiting) and only drops
+// its own stores.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -453,11 +456,12 @@ struct MergeOut {
   float* o_accum;
   __nv_bfloat16* out;
   int64_t stride_o_b, stride_o_s, stride_o_h, stride_lse_b, stride_lse_s, stride_lse_h;
+  long long* prof;         // debug timeline (see stamp), or null
 };
 __device__ __forceinline__ MergeOut merge_out_of(const AttnParams& p) {
   return MergeOut{p.cluster, p.n_splits, p.mode, p.sink, p.lse, p.lse_accum, p.o_accum, p.out,
                   p.stride_o_b, p.stride_o_s, p.stride_o_h, p.stride_lse_b, p.stride_lse_s,
-                  p.stride_lse_h};
+                  p.stride_lse_h, p.prof};
 }
 struct MergeCtx {
   uint32_t stage;          // shared address of the staging area (the K tile region)
@@ -467,31 +471,68 @@ struct MergeCtx {
   bool empty;              // this split had no tile: no TMEM, contributes zeros
 };
 
+__device__ __forceinline__ void stamp_merge(const MergeOut& p, int slot) {
+#ifdef DSV4_TIMELINE
+  if (p.prof != nullptr && (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && threadIdx.x == 0)
+    p.prof[slot] = clock64();
+#else
+  (void)p;
+  (void)slot;
+#endif
+}
+
 __device__ __noinline__ void cluster_merge(const MergeOut p, Ctrl& ctrl, const MergeCtx c,
                                            float l_own, float m_own) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int cs = p.cluster;
+  const int cs = p.cluster;                              // 2 or 4
   const uint32_t rank = cluster_rank();
   const bool final_out = p.n_splits == cs;
   const int dl = D_V / cs;                               // slice width per rank
 
+  // (1) own O^T -> own shared memory [head][d]; thread = one d (TMEM lane), 16 heads per load
   if (tid < HEADS) {
     ctrl.wred[0][tid] = l_own;
     ctrl.wred[1][tid] = m_own;
   }
-  cluster_sync_all();                                    // (1) everyone's K tile is free too
+  if (!c.empty) {
+    const int m = warp >> 2, lg = warp & 3;
+    const int d = m * 128 + lg * 32 + lane;
+#pragma unroll 1
+    for (int c4 = 0; c4 < HEADS / 16; ++c4) {
+      uint32_t o[16];
+      tmem_ld16(c.tmem_o + m * HEADS + c4 * 16, o);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(c.stage + ((c4 * 16 + i) * D_V + d) * 4), "r"(o[i]) : "memory");
+    }
+  }
+  stamp_merge(p, 240);
+  cluster_sync_all();                                    // (2)
+  stamp_merge(p, 241);
 
+  // (3) weights of all sources for head tid.  The table (4 sources x 64 heads) reuses arrays
+  // that are idle by now; wred[0] and wred[1] stay untouched, the peers are reading them.
+  float* wtab[4] = {ctrl.alpha, ctrl.wred[2], ctrl.wred[3], ctrl.mtrue};
   if (tid < HEADS) {
     const uint32_t a_l = smem_u32(&ctrl.wred[0][tid]), a_m = smem_u32(&ctrl.wred[1][tid]);
-    float big = -INFINITY;
-    for (int r = 0; r < cs; ++r) big = fmaxf(big, ld_cluster_f32(map_to_rank(a_m, r)));
-    float total = 0.f;
-    for (int r = 0; r < cs; ++r) {
-      const float mr = ld_cluster_f32(map_to_rank(a_m, r));
-      const float lr = ld_cluster_f32(map_to_rank(a_l, r));
-      if (mr != -INFINITY) total += ex2(mr - big) * lr;
+    float ms[4], ls[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      ms[r] = -INFINITY;
+      ls[r] = 0.f;
+      if (r < cs) {
+        ms[r] = ld_cluster_f32(map_to_rank(a_m, r));
+        ls[r] = ld_cluster_f32(map_to_rank(a_l, r));
+      }
     }
-    const float w_own = (m_own == -INFINITY) ? 0.f : ex2(m_own - big);
+    const float big = fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3]));
+    float w[4], total = 0.f;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      w[r] = (ms[r] == -INFINITY) ? 0.f : ex2(ms[r] - big);
+      total += w[r] * ls[r];
+    }
     float f;
     if (final_out) {
       const bool has_sink = p.sink != nullptr;
@@ -506,58 +547,65 @@ __device__ __noinline__ void cluster_merge(const MergeOut p, Ctrl& ctrl, const M
       if (rank == 0 && tid < c.heads_here && !ctrl.fail)
         p.lse_accum[c.acc_slot0 + tid] = none ? -INFINITY : logf(total) + big * LN2;
     }
-    ctrl.alpha[tid] = w_own * f;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) wtab[r][tid] = w[r] * f;
   }
   __syncthreads();
+  stamp_merge(p, 242);
 
-  // (3) push: thread = one d (TMEM lane), 16 heads per TMEM load
+  // (4) pull this rank's slice of every source, 4 consecutive d per thread; the remote
+  // loads of a batch of items all go out before the first is used (their latency is several
+  // hundred nanoseconds)
   {
-    const int m = warp >> 2, lg = warp & 3;
-    const int d = m * 128 + lg * 32 + lane;
-    const uint32_t owner = d / dl;
-    const int d_local = d - owner * dl;
-    const uint32_t dst0 = map_to_rank(c.stage + ((rank * HEADS) * dl + d_local) * 4, owner);
-#pragma unroll 1
-    for (int c4 = 0; c4 < HEADS / 16; ++c4) {
-      uint32_t o[16];
-      if (!c.empty) {
-        tmem_ld16(c.tmem_o + m * HEADS + c4 * 16, o);
-        tmem_ld_wait();
+    constexpr int BATCH = 4;
+    const int quads = dl / 4, n_items = c.heads_here * quads;
+    __nv_bfloat16* out_base = p.out + c.bi * p.stride_o_b + c.si * p.stride_o_s + c.head0 * p.stride_o_h;
+    for (int item0 = tid; item0 < n_items; item0 += BATCH * THREADS) {
+      float4 v[BATCH][4];
+#pragma unroll
+      for (int k = 0; k < BATCH; ++k) {
+        const int item = item0 + k * THREADS;
+        const int h = item / quads, q = item - h * quads;
+        const uint32_t a_loc = c.stage + (h * D_V + rank * dl + 4 * q) * 4;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          v[k][r] = make_float4(0.f, 0.f, 0.f, 0.f);
+          // weight 0: an empty split, whose memory holds nothing
+          if (item < n_items && r < cs && wtab[r][h] != 0.f) {
+            const uint32_t a = map_to_rank(a_loc, r);
+            asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(v[k][r].x), "=f"(v[k][r].y), "=f"(v[k][r].z), "=f"(v[k][r].w) : "r"(a));
+          }
+        }
       }
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int h = c4 * 16 + i;
-        const float val = c.empty ? 0.f : __uint_as_float(o[i]) * ctrl.alpha[h];
-        st_cluster_f32(dst0 + h * dl * 4, val);
+      for (int k = 0; k < BATCH; ++k) {
+        const int item = item0 + k * THREADS;
+        if (item >= n_items || ctrl.fail) continue;
+        const int h = item / quads, q = item - h * quads;
+        const int d0 = rank * dl + 4 * q;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const float w = r < cs ? wtab[r][h] : 0.f;
+          acc.x = fmaf(w, v[k][r].x, acc.x);
+          acc.y = fmaf(w, v[k][r].y, acc.y);
+          acc.z = fmaf(w, v[k][r].z, acc.z);
+          acc.w = fmaf(w, v[k][r].w, acc.w);
+        }
+        if (final_out) {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+          *reinterpret_cast<uint2*>(out_base + h * p.stride_o_h + d0) =
+              make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        } else {
+          *reinterpret_cast<float4*>(p.o_accum + (c.acc_slot0 + h) * D_V + d0) = acc;
+        }
       }
     }
   }
-  cluster_sync_all();                                    // (4) all slices have landed
-
-  // sum this rank's slice over the sources, 4 consecutive d per thread
-  if (!ctrl.fail) {
-    const int quads = dl / 4;
-    __nv_bfloat16* out_base = p.out + c.bi * p.stride_o_b + c.si * p.stride_o_s + c.head0 * p.stride_o_h;
-    for (int item = tid; item < c.heads_here * quads; item += THREADS) {
-      const int h = item / quads, q = item - h * quads;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int r = 0; r < cs; ++r) {
-        float4 v;
-        const uint32_t a = c.stage + (((r * HEADS + h) * dl) + 4 * q) * 4;
-        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a) : "memory");
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-      }
-      const int d0 = rank * dl + 4 * q;
-      if (final_out) {
-        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
-        *reinterpret_cast<uint2*>(out_base + h * p.stride_o_h + d0) =
-            make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-      } else {
-        *reinterpret_cast<float4*>(p.o_accum + (c.acc_slot0 + h) * D_V + d0) = acc;
-      }
-    }
-  }
+  stamp_merge(p, 243);
+  cluster_sync_all();                                    // (5) peers are done reading this CTA
+  stamp_merge(p, 244);
 }
 
 // ---------------------------------------------------------------------------
