@@ -398,8 +398,10 @@ def run_ours(args):
                          f"({statistics.mean(times):.2f} s per call)"}
 
     extras = {}
+    if args.extras and world > 1:
+        extras.update(run_head_tp(dev, K, ops, W, stream, rank, world, max_over_ranks))
     if args.extras and rank == 0:
-        extras = run_extras(dev, K, ops, W, stream)
+        extras.update(run_extras(dev, K, ops, W, stream))
 
     if rank == 0:
         line = {
@@ -437,10 +439,72 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def run_extras(dev, K, ops, W, stream):
-    """Secondary measurements (opt-in): the batch-64 target, one TP shard
-    (h_q = 16), the forced-128-split combine and the KV store kernel."""
+def run_head_tp(dev, K, ops, W, stream, rank, world, max_over_ranks):
+    """Head-sharded (tensor-parallel) decode of configs[1] and configs[3]: every rank holds
+    the same KV cache and index lists (MQA: one KV head), computes h_q / world heads and the
+    per-head results are exchanged with one all-gather over NVLink.  KV traffic is not
+    reduced by this sharding; the figure of interest is the time of a step."""
+    import torch.distributed as dist
+    from deepseek_v4_kernel import sharding
     out = {}
+    for name, make in (("cfg2", lambda: W.config2(dev, ops.kv_store, n_index_sets=16, seed=0)),
+                       ("cfg4", lambda: W.config4(dev, ops.kv_store, seed=0))):
+        wl = make()                                  # same seed on every rank: replicated inputs
+        hs = sharding.head_slice(wl.q.size(2), world, rank)
+        q_loc = wl.q[:, :, hs].contiguous()
+        call = K.DecodeCall(q_loc, wl.kv, wl.indices[0], wl.sm_scale, n_splits=wl.force_splits)
+        lse_loc = call.lse
+        ns = len(wl.indices)
+
+        def step(i, gather=True):
+            call.set_indices(wl.indices[i % ns])
+            call.decode(stream.cuda_stream)
+            if gather:
+                return sharding.all_gather_heads(call.out, lse_loc)
+
+        p2p = sharding.HeadGather(wl.q.size(0), 1, wl.q.size(2), dev)
+
+        def step_p2p(i, _gather=True):
+            call.set_indices(wl.indices[i % ns])
+            call.decode(stream.cuda_stream)
+            return p2p.gather(call.out, lse_loc, stream.cuda_stream)
+
+        res = {}
+        for label, gather in (("decode_plus_nccl_all_gather", True), ("decode_only", False),
+                              ("decode_plus_peer_memory_gather", None)):
+            fn = step_p2p if gather is None else step
+            for i in range(5):
+                fn(i, gather)
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for i in range(50):
+                fn(i, gather)
+            b.record(stream)
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+            res[label + "_us"] = max_over_ranks(a.elapsed_time(b)) / 50 * 1e3
+        res["peer_gather_timed_out"] = p2p.timed_out()
+        res.update(heads_per_rank=hs.stop - hs.start, n_splits=call.n_splits,
+                   gathered_bytes_per_rank=call.out.numel() * 2 + lse_loc.numel() * 4)
+        out[f"{name}_head_tp{world}"] = res
+        del wl, call
+        torch.cuda.empty_cache()
+    return out
+
+
+def run_extras(dev, K, ops, W, stream):
+    """Secondary measurements (opt-in): the other configurations of the same path.
+    Decode shapes: the batch-64 target, one TP shard (h_q = 16), the reference's own
+    584-byte layout, the single-token case, the forced-128-split long context (with its
+    combine alone).  Then sparse prefill (TFLOP/s, both KV entries) and the KV store."""
+    out = {}
+    peak, _ = measured_peaks()
+    try:
+        tf_peak = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops_sustained"]
+    except Exception:  # noqa: BLE001
+        tf_peak = 1400.0
 
     def time_calls(fn, n=50, warm=5):
         for i in range(warm):
@@ -454,22 +518,58 @@ def run_extras(dev, K, ops, W, stream):
         torch.cuda.synchronize(dev)
         return a.elapsed_time(b) / n
 
-    peak, _ = measured_peaks()
-    for name in ("target", "cfg2_tp16"):
-        params, _ = workload_params(name)
-        wl = W.config2(dev, ops.kv_store, n_index_sets=4 if name == "target" else 16, **params)
-        call = K.DecodeCall(wl.q, wl.kv, wl.indices[0], wl.sm_scale)
+    def decode_case(name, wl, n_splits=None):
+        call = K.DecodeCall(wl.q, wl.kv, wl.indices[0], wl.sm_scale, n_splits=n_splits)
         ns = len(wl.indices)
 
-        def fn(i, call=call, wl=wl, ns=ns):
+        def fn(i):
             call.set_indices(wl.indices[i % ns])
             call.decode(stream.cuda_stream)
         ms = time_calls(fn)
         gbs = wl.algorithmic_bytes() / (ms * 1e-3) / 1e9
         out[name] = {"us_per_call": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peak,
-                     "n_splits": call.n_splits}
-        del wl, call
+                     "n_splits": call.n_splits, "partial_sets": call.partial_sets}
+        return call
+
+    for name in ("target", "cfg2_tp16"):
+        params, _ = workload_params(name)
+        wl = W.config2(dev, ops.kv_store, n_index_sets=4 if name == "target" else 16, **params)
+        decode_case(name, wl)
+        del wl
         torch.cuda.empty_cache()
+    wl = W.config2(dev, ops.kv_store, n_index_sets=16, layout="MODEL1")
+    decode_case("cfg2_layout_584B", wl)
+    del wl
+    wl = W.config1(dev, ops.kv_store)
+    decode_case("cfg1", wl)
+    del wl
+    wl = W.config4(dev, ops.kv_store)
+    call = decode_case("cfg4_128_splits", wl, n_splits=wl.force_splits)
+    if call.partial_sets > 1:
+        ms = time_calls(lambda i: call.combine(stream.cuda_stream))
+        b_, h_q = wl.q.size(0), wl.q.size(2)
+        cbytes = call.partial_sets * b_ * h_q * (512 * 4 + 4) + b_ * h_q * (512 * 2 + 4)
+        out["cfg4_combine_alone"] = {"us_per_call": ms * 1e3, "gbs": cbytes / (ms * 1e-3) / 1e9,
+                                     "bytes": cbytes, "partial_sets": call.partial_sets}
+    del wl, call
+    torch.cuda.empty_cache()
+
+    # sparse prefill (configs[4]): s_q = s_kv = 8192, causal top-2048
+    pw = W.config5(dev, ops.kv_store)
+    for name, fn in (("cfg5_prefill_bf16_kv", lambda i: ops.sparse_prefill_fwd(pw.q, pw.kv_bf16, pw.indices, pw.sm_scale, 512)),
+                     ("cfg5_prefill_fp8_pages", lambda i: ops.sparse_prefill_fwd_fp8(pw.q, pw.kv_pages, pw.indices, pw.sm_scale, 512))):
+        ms = time_calls(fn, n=5, warm=2)
+        tf = pw.flops() / (ms * 1e-3) / 1e12
+        out[name] = {"ms_per_call": ms, "tflops": tf, "frac_of_measured_bf16_sustained": tf / tf_peak,
+                     "pairs": pw.pairs()}
+    # KV store / quantise of the same 8192 tokens
+    d_nope = pw.kv_bf16.size(1) - 64
+    k_nope, k_rope = pw.kv_bf16[:, :d_nope].contiguous(), pw.kv_bf16[:, d_nope:].contiguous()
+    slots = torch.arange(pw.q.size(0), device=dev, dtype=torch.int64)
+    ms = time_calls(lambda i: ops.kv_store(k_nope, k_rope, slots, pw.kv_pages), n=50)
+    sbytes = pw.q.size(0) * (d_nope * 2 + 128 + 644)      # BF16 in, one 644-byte token out
+    out["kv_store_8192_tokens"] = {"us_per_call": ms * 1e3, "gbs": sbytes / (ms * 1e-3) / 1e9,
+                                   "frac_of_measured_hbm": sbytes / (ms * 1e-3) / 1e9 / peak}
     return out
 
 

@@ -17,7 +17,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.environ.get("DSV4_BUILD_OUT") or os.path.join(HERE, "deepseek_v4_kernel", "libdsv4_b200.so")
 SOURCES = ["capi.cu", "simple_kernels.cu", "umma_selftest.cu", "sparse_attn_sm100.cu",
-           "noalloc_entry.cu"]
+           "noalloc_entry.cu", "head_gather.cu"]
 
 
 def _stale() -> bool:

@@ -358,6 +358,20 @@ int dsv4_device_status(int32_t* status_out, int reset) {
   return DSV4_OK;
 }
 
+int dsv4_gather_heads(const Dsv4GatherArgs* a, void* stream) {
+  if (!a || !a->out_local || !a->lse_local || !a->counter || !a->status) return DSV4_ERR_NULL;
+  if (a->world < 1 || a->world > DSV4_MAX_PEERS || a->rank < 0 || a->rank >= a->world || a->b < 0 ||
+      a->s_q < 1 || a->h_local < 1)
+    return DSV4_ERR_SHAPE;
+  for (int r = 0; r < a->world; ++r) {
+    if (!a->peer_out[r] || !a->peer_lse[r] || !a->peer_flags[r]) return DSV4_ERR_NULL;
+    if (!aligned16(a->peer_out[r])) return DSV4_ERR_ALIGN;
+  }
+  if (!aligned16(a->out_local)) return DSV4_ERR_ALIGN;
+  cudaError_t e = dsv4::launch_gather_heads(*a, static_cast<cudaStream_t>(stream));
+  return e ? cuda_fail(e) : DSV4_OK;
+}
+
 int dsv4_umma_selftest(int mode, int n, int k, const void* a, const void* b, float* d,
                        int32_t* status, void* stream) {
   if (!a || !b || !d || !status) return DSV4_ERR_NULL;

@@ -41,6 +41,7 @@ cudaError_t launch_gather_dequant(const void* kv, int64_t stride, int kv_format,
 bool sm100_attn_supported(int kv_format, int d_qk);
 cudaError_t launch_sm100_attn(const AttnParams& p, int kv_format, int d_qk, cudaStream_t st);
 cudaError_t read_attn_error(int* value, bool reset);
+cudaError_t launch_gather_heads(const Dsv4GatherArgs& a, cudaStream_t st);
 cudaError_t launch_umma_selftest(int mode, int n, int k, const void* a, const void* b, float* d,
                                  int32_t* status, cudaStream_t st);
 

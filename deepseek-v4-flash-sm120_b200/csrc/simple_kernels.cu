@@ -165,7 +165,7 @@ simple_attn_kernel(AttnParams p) {
 constexpr int COMBINE_WARPS = 8;
 constexpr int COMBINE_MAX_SPLITS = 256;
 constexpr int COMBINE_PARTS = 4;          // warps sharing one (row, head): 128 columns each
-constexpr int COMBINE_BATCH = 8;          // partial rows in flight per thread
+constexpr int COMBINE_BATCH = 16;         // partial rows in flight per thread
 
 // Warp (row, head, part) merges columns [128 part, 128 part + 128) of the n_splits partial
 // rows: every lane owns one float4 per split and keeps COMBINE_BATCH loads in flight.

@@ -32,6 +32,16 @@ class DecodeArgs(C.Structure):
                 "stride_o_h", "stride_lse_b", "stride_lse_s", "stride_lse_h")]
 
 
+MAX_PEERS = 8
+
+
+class GatherArgs(C.Structure):
+    _fields_ = [(n, i32) for n in ("world", "rank", "b", "s_q", "h_local", "step")] + [
+        ("out_local", vp), ("lse_local", vp), ("peer_out", vp * MAX_PEERS),
+        ("peer_lse", vp * MAX_PEERS), ("peer_flags", vp * MAX_PEERS), ("counter", vp),
+        ("status", vp)]
+
+
 class CombineArgs(C.Structure):
     _fields_ = [(n, i32) for n in ("n_rows", "s_q", "h_q", "n_splits")] + [(n, vp) for n in (
         "o_accum", "lse_accum", "attn_sink", "out", "lse")] + [(n, i64) for n in (
@@ -62,6 +72,7 @@ SYMBOLS = {
     "dsv4_device_info": (C.c_int, [C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int),
                                    C.POINTER(C.c_int)]),
     "dsv4_plan_splits": (C.c_int, [C.c_int] * 6),
+    "dsv4_gather_heads": (C.c_int, [C.POINTER(GatherArgs), C.c_void_p]),
     "dsv4_decode_partial_sets": (C.c_int, [C.POINTER(DecodeArgs)]),
     "dsv4_sparse_decode": (C.c_int, [C.POINTER(DecodeArgs), vp]),
     "dsv4_sparse_decode_noalloc": (C.c_int, [C.POINTER(DecodeArgs), vp]),

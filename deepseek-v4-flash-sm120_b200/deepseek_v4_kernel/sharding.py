@@ -69,3 +69,85 @@ def all_gather_heads(out_local: torch.Tensor, lse_local: torch.Tensor, group=Non
     out = out_all.permute(1, 2, 0, 3, 4).reshape(b, s_q, world * h_loc, d)
     lse = lse_all.permute(1, 0, 2, 3).reshape(b, world * h_loc, s_q)
     return out, lse
+
+
+class HeadGather:
+    """All-gather of head-sharded decode results through NVLink peer memory
+    (`dsv4_gather_heads`): one kernel per rank instead of two library collectives.
+
+    The gathered buffers live in symmetric memory (every rank maps every rank's copy).
+    Two buffer sets alternate between steps; `gather` returns views of the set just
+    filled, valid until the call after next.  All ranks must call `gather` the same
+    number of times.  CUDA only; needs the in-tree library and peer access between the
+    GPUs of the group.
+    """
+
+    def __init__(self, b: int, s_q: int, h_q: int, device, group=None):
+        import ctypes as C
+        import os
+        # plain peer loads and stores only: no NVLink multicast object is bound to the buffers
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+        from . import _native as N
+        self._N, self._C = N, C
+        group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if h_q % self.world:
+            raise ValueError(f"h_q={h_q} is not divisible by the tensor-parallel size {self.world}")
+        if self.world > N.MAX_PEERS:
+            raise ValueError(f"at most {N.MAX_PEERS} ranks")
+        self.b, self.s_q, self.h_q, self.h_local = b, s_q, h_q, h_q // self.world
+        out_bytes = b * s_q * h_q * 512 * 2
+        lse_bytes = (b * h_q * s_q * 4 + 255) // 256 * 256
+        set_bytes = out_bytes + lse_bytes
+        self._offsets = [(k * set_bytes, k * set_bytes + out_bytes) for k in range(2)]
+        self._flag_off = 2 * set_bytes
+        total = self._flag_off + 256
+        self.buf = symm.empty(total, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        torch.cuda.synchronize(device)
+        self.hdl = symm.rendezvous(self.buf, group.group_name)
+        self.peer_base = [int(p) for p in self.hdl.buffer_ptrs]
+        self.counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.step = 0
+        self.views = []
+        for o_off, l_off in self._offsets:
+            out = self.buf[o_off:o_off + out_bytes].view(torch.bfloat16).view(b, s_q, h_q, 512)
+            lse = self.buf[l_off:l_off + b * h_q * s_q * 4].view(torch.float32).view(b, h_q, s_q)
+            self.views.append((out, lse))
+        dist.barrier(group)                     # every rank has zeroed its flags before any step
+        torch.cuda.synchronize(device)
+
+    def _args_for(self, k: int):
+        N = self._N
+        a = N.GatherArgs()
+        a.world, a.rank, a.b, a.s_q, a.h_local = self.world, self.rank, self.b, self.s_q, self.h_local
+        o_off, l_off = self._offsets[k]
+        for r in range(self.world):
+            a.peer_out[r] = self.peer_base[r] + o_off
+            a.peer_lse[r] = self.peer_base[r] + l_off
+            a.peer_flags[r] = self.peer_base[r] + self._flag_off
+        a.counter, a.status = self.counter.data_ptr(), self.status.data_ptr()
+        return a
+
+    def gather(self, out_local: torch.Tensor, lse_local: torch.Tensor, stream: int):
+        """Queue the exchange of this rank's shard on `stream`; returns (out, lse) views of
+        the gathered buffers [b, s_q, h_q, 512] / [b, h_q, s_q], complete once the kernel
+        has run."""
+        if not hasattr(self, "_args"):
+            self._args = [self._args_for(0), self._args_for(1)]
+        assert out_local.is_contiguous() and lse_local.is_contiguous()
+        self.step += 1
+        k = self.step & 1
+        a = self._args[k]
+        a.step = self.step
+        a.out_local, a.lse_local = out_local.data_ptr(), lse_local.data_ptr()
+        rc = self._N.lib.dsv4_gather_heads(self._C.byref(a), stream)
+        if rc:
+            self._N.check(rc, "dsv4_gather_heads")
+        return self.views[k]
+
+    def timed_out(self) -> bool:
+        """True when a bounded wait for a peer's shard ran out (synchronises)."""
+        return bool(self.status.item() != 0)

@@ -156,6 +156,38 @@ int dsv4_plan_splits(int b, int s_q, int h_q, int topk, int extra_topk, int num_
 int dsv4_decode_partial_sets(const Dsv4DecodeArgs* args);
 
 /* ---------------------------------------------------------------------------
+ * All-gather of head-sharded decode results over NVLink peer memory (tensor
+ * parallel over heads: every GPU runs dsv4_sparse_decode on h_q / world heads of
+ * the same requests).  Stands in for the two NCCL all-gathers a head-sharded
+ * caller of the reference would issue after sparse_decode_fwd; the reference
+ * itself has no multi-GPU code.
+ *
+ * peer_out[r] / peer_lse[r] / peer_flags[r] are rank r's gathered buffers
+ * (BF16 [b, s_q, h_local*world, 512], fp32 [b, h_local*world, s_q], int32[world],
+ * flags zero-initialised) as mapped into THIS process (peer-mapped device memory,
+ * e.g. CUDA IPC or symmetric memory); entry `rank` is the local one.  `step` must
+ * increase by one per call and the caller must alternate between two sets of
+ * gathered buffers (the flag array is shared by both).  `counter` is a local
+ * zero-initialised int32, `status` a local int32 that receives a non-zero code
+ * when a peer's shard did not arrive within the bounded wait (~0.3 s).
+ * All ranks must call it for the same step; the kernel returns once every shard
+ * has landed locally.  No host synchronisation.
+ * ------------------------------------------------------------------------- */
+#define DSV4_MAX_PEERS 8
+typedef struct Dsv4GatherArgs {
+  int32_t world, rank, b, s_q, h_local, step;
+  const void* out_local;        /* BF16 [b, s_q, h_local, 512], dense              */
+  const float* lse_local;       /* fp32 [b, h_local, s_q], dense                   */
+  void* peer_out[DSV4_MAX_PEERS];
+  float* peer_lse[DSV4_MAX_PEERS];
+  int32_t* peer_flags[DSV4_MAX_PEERS];
+  int32_t* counter;
+  int32_t* status;
+} Dsv4GatherArgs;
+
+int dsv4_gather_heads(const Dsv4GatherArgs* args, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------
  * Split-KV combine alone: replaces dsv4_split_kv_combine
  * (csrc/sm120/decode/split_kv_combine.cuh:23-110).
  * o_accum fp32 [n_splits, n_rows, h_q, 512] and lse_accum fp32
