@@ -164,18 +164,21 @@ simple_attn_kernel(AttnParams p) {
 // ---------------------------------------------------------------------------
 constexpr int COMBINE_WARPS = 8;
 constexpr int COMBINE_MAX_SPLITS = 256;
-constexpr int COMBINE_PARTS = 4;          // warps sharing one (row, head): 128 columns each
 constexpr int COMBINE_BATCH = 16;         // partial rows in flight per thread
 
-// Warp (row, head, part) merges columns [128 part, 128 part + 128) of the n_splits partial
-// rows: every lane owns one float4 per split and keeps COMBINE_BATCH loads in flight.
+// Warp (row, head, part) merges columns [part, part + 1) * 32 * VEC of the n_splits partial
+// rows: every lane owns VEC consecutive floats per split and keeps COMBINE_BATCH loads in
+// flight.  VEC = 4 (four warps per head) when there are many (row, head) pairs, VEC = 1
+// (sixteen warps per head) when there are few, so that the grid still fills the GPU.
+template <int VEC>
 __global__ void __launch_bounds__(COMBINE_WARPS * 32)
 combine_kernel(Dsv4CombineArgs a) {
+  constexpr int PARTS = D_V / (32 * VEC);
   __shared__ float s_w[COMBINE_WARPS][COMBINE_MAX_SPLITS];
   grid_dependency_wait();                 // the partials come from the kernel just before
   const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int unit = blockIdx.y * COMBINE_WARPS + warp;
-  const int h = unit / COMBINE_PARTS, part = unit % COMBINE_PARTS;
+  const int h = unit / PARTS, part = unit % PARTS;
   if (h >= a.h_q) return;
   const int64_t rows_h = static_cast<int64_t>(a.n_rows) * a.h_q;
   const int64_t slot0 = static_cast<int64_t>(row) * a.h_q + h;
@@ -201,33 +204,46 @@ combine_kernel(Dsv4CombineArgs a) {
   if (lane == 0 && part == 0)
     a.lse[bi * a.stride_lse_b + si * a.stride_lse_s + h * a.stride_lse_h] = lse_v;
 
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  const float4* src = reinterpret_cast<const float4*>(a.o_accum + slot0 * D_V) + part * 32 + lane;
-  const int64_t split_stride4 = rows_h * D_V / 4;
+  float acc[VEC];
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+  const int col = (part * 32 + lane) * VEC;
+  const float* src = a.o_accum + slot0 * D_V + col;
+  const int64_t split_stride = rows_h * D_V;
   for (int s0 = 0; s0 < a.n_splits; s0 += COMBINE_BATCH) {
-    float4 v[COMBINE_BATCH];
+    float v[COMBINE_BATCH][VEC];
     float w[COMBINE_BATCH];
 #pragma unroll
     for (int k = 0; k < COMBINE_BATCH; ++k) {
       const int s = s0 + k;
       w[k] = s < a.n_splits ? s_w[warp][s] : 0.f;
-      v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (w[k] != 0.f) v[k] = __ldg(src + s * split_stride4);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) v[k][j] = 0.f;
+      if (w[k] != 0.f) {
+        if constexpr (VEC == 4) {
+          const float4 t = __ldg(reinterpret_cast<const float4*>(src + s * split_stride));
+          v[k][0] = t.x; v[k][1] = t.y; v[k][2] = t.z; v[k][3] = t.w;
+        } else {
+          v[k][0] = __ldg(src + s * split_stride);
+        }
+      }
     }
 #pragma unroll
     for (int k = 0; k < COMBINE_BATCH; ++k) {       // fixed order: the result does not depend on timing
-      acc.x = fmaf(w[k], v[k].x, acc.x);
-      acc.y = fmaf(w[k], v[k].y, acc.y);
-      acc.z = fmaf(w[k], v[k].z, acc.z);
-      acc.w = fmaf(w[k], v[k].w, acc.w);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) acc[j] = fmaf(w[k], v[k][j], acc[j]);
     }
   }
   __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(a.out) + bi * a.stride_o_b +
-                        si * a.stride_o_s + h * a.stride_o_h;
-  __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * f, acc.y * f);
-  __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * f, acc.w * f);
-  *reinterpret_cast<uint2*>(orow + (part * 32 + lane) * 4) =
-      make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                        si * a.stride_o_s + h * a.stride_o_h + col;
+  if constexpr (VEC == 4) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc[0] * f, acc[1] * f);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(acc[2] * f, acc[3] * f);
+    *reinterpret_cast<uint2*>(orow) =
+        make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+  } else {
+    *orow = __float2bfloat16_rn(acc[0] * f);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -350,14 +366,19 @@ cudaError_t launch_simple_attn(const AttnParams& p, int kv_format, int d_qk, cud
 }
 
 cudaError_t launch_combine(const Dsv4CombineArgs& a, cudaStream_t st) {
+  // Four warps per (row, head) give n_rows * h_q / 2 CTAs; below about two CTAs per SM
+  // (B200: 148 SMs) sixteen warps per (row, head) are used instead.
+  const bool fine = static_cast<int64_t>(a.n_rows) * a.h_q < 600;
+  const int parts = fine ? 16 : 4;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(a.n_rows, (a.h_q * COMBINE_PARTS + COMBINE_WARPS - 1) / COMBINE_WARPS);
+  cfg.gridDim = dim3(a.n_rows, (a.h_q * parts + COMBINE_WARPS - 1) / COMBINE_WARPS);
   cfg.blockDim = dim3(COMBINE_WARPS * 32);
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   cfg.attrs = attr;
   cfg.numAttrs = add_overlap_attribute(attr);
-  return cudaLaunchKernelEx(&cfg, combine_kernel, a);
+  return fine ? cudaLaunchKernelEx(&cfg, combine_kernel<1>, a)
+              : cudaLaunchKernelEx(&cfg, combine_kernel<4>, a);
 }
 
 int combine_max_splits() { return COMBINE_MAX_SPLITS; }
