@@ -316,12 +316,20 @@ __device__ __forceinline__ void load_half(uint4 (&d)[Stage<FMT, DQK>::LINES], co
   using S = Stage<FMT, DQK>;
   const uint8_t* scl;
   const uint8_t* row = row_ptr<FMT>(cache_of<EXTRA>(p, lv, j), idx, scl);
+  if (row == nullptr) {                  // the entry names no row: a row of zeros
+#pragma unroll
+    for (int c = 0; c < S::LINES; ++c) d[c] = make_uint4(0, 0, 0, 0);
+    return;
+  }
 #pragma unroll
   for (int c = 0; c < S::LINES; ++c) {
     const int piece = S::copied_line(c) ? geo.piece_cp : geo.piece;
-    d[c] = make_uint4(0, 0, 0, 0);
-    const bool in_row = (8 * c + 7 < S::CH) || (8 * c + piece < S::CH);
-    if (row != nullptr && in_row) d[c] = ldg16(row + 16 * piece + 128 * c);
+    if constexpr (8 * (S::LINES - 1) + 7 < S::CH) {
+      d[c] = ldg16(row + 16 * piece + 128 * c);       // every line is full
+    } else {
+      d[c] = make_uint4(0, 0, 0, 0);
+      if (8 * c + 7 < S::CH || 8 * c + piece < S::CH) d[c] = ldg16(row + 16 * piece + 128 * c);
+    }
   }
 }
 
@@ -339,7 +347,8 @@ __device__ __forceinline__ void load_one_line(uint4& d, int line, const AttnPara
 
 // Convert and store line LINE of the staged row `v` (tile row `row`).  `mul_row` holds the
 // row's entries of the multiplier table: per scale byte s a pair of packed-BF16 factors,
-// (2^(s-7), 0) normally, (2^120, 2^(s-127)) for s = 0 or s > 134.
+// (2^(s-7), 1) normally, (2^120, 2^(s-127)) for s = 0 or s > 134.  Both multiplies are always
+// done (the second is exact either way): straight-line code beats a branch per line here.
 template <int FMT, int DQK, int LINE>
 __device__ __forceinline__ void store_line(const uint4& v, uint32_t sK, int row, const Geo& geo,
                                            const uint32_t (&mul_row)[Cfg<FMT, DQK>::MUL_PER_ROW + 2]) {
@@ -366,10 +375,8 @@ __device__ __forceinline__ void store_line(const uint4& v, uint32_t sK, int row,
       dequant4_one_mul(v.y, c1, o[2], o[3]);
       dequant4_one_mul(v.z, c1, o[4], o[5]);
       dequant4_one_mul(v.w, c1, o[6], o[7]);
-      if (c2 != 0) {                                            // rare scale bytes
 #pragma unroll
-        for (int k = 0; k < 8; ++k) o[k] = bf16x2_mul(o[k], c2);
-      }
+      for (int k = 0; k < 8; ++k) o[k] = bf16x2_mul(o[k], c2);  // 1.0 except for rare scale bytes
       const uint32_t a = rbase + (ci >> 2) * KBLOCK_BYTES + (((2 * (ci & 3)) ^ x) << 4);
       st_shared_v4(a, o[0], o[1], o[2], o[3]);
       st_shared_v4(a ^ 16, o[4], o[5], o[6], o[7]);             // the neighbouring chunk
@@ -752,7 +759,7 @@ sm100_attn_kernel(const AttnParams p) {
         for (int k = 0; k < T::N_SCALE; ++k) {
           const ScaleMul m = make_scale_mul((sw.w[k >> 2] >> (8 * (k & 3))) & 0xffu);
           dst[2 * k] = m.c1;
-          dst[2 * k + 1] = m.c2;
+          dst[2 * k + 1] = m.c2 ? m.c2 : 0x3F803F80u;           // packed BF16 1.0
         }
       }
     }
