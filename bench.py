@@ -325,7 +325,7 @@ def run_ours(args):
     # duplex).  Nothing is skipped or reused between steps.
     q_host = wl.q.cpu().pin_memory()
     idx_host = [t.cpu().pin_memory() for t in wl.indices]
-    NBUF = 3
+    NBUF = int(os.environ.get("DSV4_BENCH_E2E_STREAMS", "3"))
     out_host = [torch.empty((params["b"], 1, params["h_q"], 512), dtype=torch.bfloat16).pin_memory()
                 for _ in range(NBUF)]
     lse_host = [torch.empty((params["b"], params["h_q"], 1), dtype=torch.float32).pin_memory()
