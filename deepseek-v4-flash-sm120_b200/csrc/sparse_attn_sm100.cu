@@ -833,32 +833,39 @@ sm100_attn_kernel(const AttnParams p) {
   const uint64_t dQ = make_smem_desc(sQ, 16, 1024, SWZ_128B);
   const uint64_t dV = make_smem_desc(sK, KBLOCK_BYTES, 1024, SWZ_128B);  // MN-major view
   const uint64_t dP = make_smem_desc(sP, 1024, 1024, SWZ_128B);
-  const uint32_t dK_lo = static_cast<uint32_t>(dK), dK_hi = static_cast<uint32_t>(dK >> 32);
-  const uint32_t dQ_lo = static_cast<uint32_t>(dQ), dQ_hi = static_cast<uint32_t>(dQ >> 32);
-  const uint32_t dV_lo = static_cast<uint32_t>(dV), dV_hi = static_cast<uint32_t>(dV >> 32);
-  const uint32_t dP_lo = static_cast<uint32_t>(dP), dP_hi = static_cast<uint32_t>(dP >> 32);
+  // Both issue routines are run by the whole issuing warp, converged; one elected lane
+  // issues the MMAs and the commits (see umma_bf16_elect).
+  const uint32_t elected = elect_one();
+  const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
   auto issue_qk = [&](int t, bool& ok) {
-    if (ok && !mbar_wait(bar_k_full, t & 1)) { atomicExch(&g_attn_error, ERR_KFULL); ok = false; }
+    if (ok && !mbar_wait_warp(bar_k_full, t & 1, lane)) { atomicExch(&g_attn_error, ERR_KFULL); ok = false; }
     tc_fence_after_sync();
-    TSTAMP(t, 1);
+    if (lane == 0) TSTAMP(t, 1);
 #pragma unroll 1
-    for (int kb = 0; kb < C::NB; ++kb)       // four 16-wide steps of one 64-column block
-      umma_bf16_x4(tmem + COL_S, 0, dK_lo + ((kb * KBLOCK_BYTES) >> 4), dK_hi, 2,
-                   dQ_lo + ((kb * QBLOCK_BYTES) >> 4), dQ_hi, 2, idesc_qk, kb != 0, 1);
-    umma_commit(bar_s_full);
+    for (int kb = 0; kb < C::NB; ++kb) {     // four 16-wide steps of one 64-column block
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4)
+        umma_bf16_elect(tmem_u + COL_S, dK + static_cast<uint64_t>((kb * KBLOCK_BYTES + k4 * 32) >> 4),
+                        dQ + static_cast<uint64_t>((kb * QBLOCK_BYTES + k4 * 32) >> 4), idesc_qk,
+                        (kb | k4) != 0, elected);
+    }
+    umma_commit_elect(bar_s_full, elected);
   };
   auto issue_pv = [&](int t, bool last, bool& ok) {
-    if (ok && !mbar_wait(bar_p_full, t & 1)) { atomicExch(&g_attn_error, ERR_PFULL); ok = false; }
+    if (ok && !mbar_wait_warp(bar_p_full, t & 1, lane)) { atomicExch(&g_attn_error, ERR_PFULL); ok = false; }
     tc_fence_after_sync();
-    TSTAMP(t, 5);
+    if (lane == 0) TSTAMP(t, 5);
 #pragma unroll 1
     for (int j = 0; j < KSTEPS; ++j) {       // the four 128-row slices of O^T for one k-step
       const uint32_t acc = (t | j) != 0;
-      umma_bf16_x4(tmem + COL_O, HEADS, dV_lo + ((j * 2048) >> 4), dV_hi, (2 * KBLOCK_BYTES) >> 4,
-                   dP_lo + ((j * 2048) >> 4), dP_hi, 0, idesc_pv, acc, acc);
-      umma_commit(bar_kv_free0 + 8 * j);
+#pragma unroll
+      for (int mb = 0; mb < 4; ++mb)
+        umma_bf16_elect(tmem_u + COL_O + mb * HEADS,
+                        dV + static_cast<uint64_t>((j * 2048 + mb * 2 * KBLOCK_BYTES) >> 4),
+                        dP + static_cast<uint64_t>((j * 2048) >> 4), idesc_pv, acc, elected);
+      umma_commit_elect(bar_kv_free0 + 8 * j, elected);
     }
-    if (last) umma_commit(bar_o_done);
+    if (last) umma_commit_elect(bar_o_done, elected);
   };
 
   // ---- refill of the K tile from the staged registers -------------------------------
@@ -962,8 +969,7 @@ sm100_attn_kernel(const AttnParams p) {
   for (int t = -1; t < n_tiles; ++t) {
     const bool more = t + 1 < n_tiles;
     if (t >= 0) {
-    if (tid == ISSUE_TID) issue_qk(t, ok);
-    __syncwarp();
+    if (warp == ISSUE_WARP) issue_qk(t, ok);
     if (t + 2 < n_tiles) {                       // list entries of the tile after next
       const int j2 = lv.begin + (t + 2) * TILE;
       tidx_next[0] = list_index<EXTRA>(lv, j2 + geo.row(0));
@@ -1077,8 +1083,7 @@ sm100_attn_kernel(const AttnParams p) {
     __syncwarp();
     if (lane == 0) mbar_arrive(bar_p_full);
     if (tid == 0) TSTAMP(t, 4);
-    if (tid == ISSUE_TID) issue_pv(t, !more, ok);
-    __syncwarp();
+    if (warp == ISSUE_WARP) issue_pv(t, !more, ok);
 
     }  // t >= 0
 
