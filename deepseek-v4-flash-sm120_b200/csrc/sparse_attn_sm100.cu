@@ -913,17 +913,16 @@ sm100_attn_kernel(const AttnParams p) {
     }
     const bool reload = has_next && !spared;
     if constexpr (S::HALVES == 2) {
-      // Both k-steps are staged.  The first register set is reloaded as soon as it has been
-      // stored, the second once this warp's part of the tile is published: that spreads the
-      // gather over the P.V phase (all SMs gather in step, and a burst holds the issuing
-      // warps up for as long as HBM takes to serve it) and keeps it out of the way of k_full.
+      // Both k-steps are staged.  Each register set is reloaded as soon as it has been stored:
+      // that spreads the gather over the P.V phase (all SMs gather in step, and a burst holds
+      // the issuing warps up for as long as HBM takes to serve it).
 #pragma unroll
       for (int jhalf = 0; jhalf < 2; ++jhalf) {
         wait_free(4 * jhalf + geo.jsub);
         if (lane == 0 && wait_tile == 2) stamp(p, 150 + 32 * jhalf + warp);       // k-step free
         store_set(stage.d[jhalf], geo.row(jhalf));
-        if (reload && jhalf == 0)          // the same rows of the next tile
-          load_half<FMT, DQK, EXTRA>(stage.d[0], p, lv, j0 + TILE + geo.row(0), tidx_next[0], geo);
+        if (reload)                        // the same rows of the next tile
+          load_half<FMT, DQK, EXTRA>(stage.d[jhalf], p, lv, j0 + TILE + geo.row(jhalf), tidx_next[jhalf], geo);
       }
       if (extra) {                         // this warp's line of the issuing warp's rows
         wait_free(xk);
@@ -933,8 +932,6 @@ sm100_attn_kernel(const AttnParams p) {
       }
       publish();
       if (lane == 0 && wait_tile == 2) stamp(p, 214 + warp);                     // arrived
-      if (reload)
-        load_half<FMT, DQK, EXTRA>(stage.d[1], p, lv, j0 + TILE + geo.row(1), tidx_next[1], geo);
       if (has_x && has_next)
         load_one_line<FMT, DQK, EXTRA>(xd, xline, p, lv, j0 + TILE + xrow, xidx_next, geo);
     } else {
