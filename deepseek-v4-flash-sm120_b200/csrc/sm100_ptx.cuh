@@ -130,48 +130,6 @@ __device__ __forceinline__ void umma_commit_elect(uint32_t bar, uint32_t elected
       "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
       ::"r"(bar), "r"(elected) : "memory");
 }
-// Same, with each descriptor given as its low and high 32-bit words so that stepping
-// the start address costs one 32-bit add.
-__device__ __forceinline__ void umma_bf16_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi,
-                                               uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
-                                               uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-      "mov.b64 da, {%1, %2};\n\t"
-      "mov.b64 db, {%3, %4};\n\t"
-      "setp.ne.b32 p, %6, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
-      ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Four MMAs in one go: descriptor start addresses a_lo + i * a_step, b_lo + i * b_step
-// (steps in 16-byte units), destinations tmem_d + i * d_step columns.  The first one
-// accumulates only if `acc_first` is non-zero; the rest accumulate iff `acc_rest`.
-// One predicate set-up and three instructions per MMA keep the issuing thread fast.
-__device__ __forceinline__ void umma_bf16_x4(uint32_t tmem_d, uint32_t d_step, uint32_t a_lo,
-                                             uint32_t a_hi, uint32_t a_step, uint32_t b_lo,
-                                             uint32_t b_hi, uint32_t b_step, uint32_t idesc,
-                                             uint32_t acc_first, uint32_t acc_rest) {
-  asm volatile(
-      "{\n\t.reg .pred p0, p1;\n\t.reg .b64 da, db;\n\t.reg .b32 ta, tb, td;\n\t"
-      "setp.ne.b32 p0, %9, 0;\n\t"
-      "setp.ne.b32 p1, %10, 0;\n\t"
-      "mov.b64 da, {%2, %3};\n\t"
-      "mov.b64 db, {%5, %6};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %8, p0;\n\t"
-      "add.u32 ta, %2, %4;\n\t add.u32 tb, %5, %7;\n\t add.u32 td, %0, %1;\n\t"
-      "mov.b64 da, {ta, %3};\n\t mov.b64 db, {tb, %6};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [td], da, db, %8, p1;\n\t"
-      "add.u32 ta, ta, %4;\n\t add.u32 tb, tb, %7;\n\t add.u32 td, td, %1;\n\t"
-      "mov.b64 da, {ta, %3};\n\t mov.b64 db, {tb, %6};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [td], da, db, %8, p1;\n\t"
-      "add.u32 ta, ta, %4;\n\t add.u32 tb, tb, %7;\n\t add.u32 td, td, %1;\n\t"
-      "mov.b64 da, {ta, %3};\n\t mov.b64 db, {tb, %6};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [td], da, db, %8, p1;\n\t}"
-      ::"r"(tmem_d), "r"(d_step), "r"(a_lo), "r"(a_hi), "r"(a_step), "r"(b_lo), "r"(b_hi),
-        "r"(b_step), "r"(idesc), "r"(acc_first), "r"(acc_rest)
-      : "memory");
-}
 // Arrive on an mbarrier once all MMAs issued so far by this thread complete.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
@@ -236,12 +194,6 @@ __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-// Maximum of a float over the 32 lanes of the warp, returned to every lane.
-__device__ __forceinline__ float warp_max_f32(float v) {
-  float r;
-  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
-  return r;
-}
 
 __device__ __forceinline__ uint32_t elect_one() {
   uint32_t pred;

@@ -13,27 +13,32 @@
 // (contraction over d) for the first product and as MN-major (contraction over
 // tokens) for the second.  With d_qk = 576 the tile (144 KB) and Q (72 KB) leave
 // no room for a second tile or a staging ring, so gathered rows are staged in
-// REGISTERS: the tile is cut into units of four rows x one 128-byte line dealt
-// round-robin to the warps; a warp issues the 16-byte loads of the next tile
-// while the current one is being multiplied, and writes each 16-row "k-step"
-// (dequantised to BF16) as soon as the P.V MMA step that last read those rows
-// has retired.  P^T
-// (16 KB) reuses the RoPE block of the tile, which only Q.K^T reads, when
-// d_qk = 576.
+// REGISTERS: a tile is 8 "k-steps" of 16 rows; every warp owns four rows of two
+// k-steps, issues their 16-byte loads a tile ahead, and converts and writes them
+// (dequantised to BF16) as soon as the P.V MMA step that last read those rows has
+// retired.  P^T (16 KB) reuses the RoPE block of the tile, which only Q.K^T
+// reads, when d_qk = 576.
 //
 // All 16 warps are alike (512 threads x 128 registers = the whole register
-// file) and move through the phases of a tile together: issue next tile's loads
-// -> softmax of S^T (thread = one tile row = one TMEM lane, 16 of the 64 heads)
-// -> refill the K tile behind the P.V product.  Thread 0 also issues the MMAs,
-// which run asynchronously and report through mbarriers; warp 0 owns TMEM.
+// file) and move through the phases of a tile together: softmax of S^T (thread
+// = one tile row = one TMEM lane, 16 of the 64 heads) -> refill the K tile behind
+// the P.V product and reload the registers for the tile after.  The last warp
+// also issues the MMAs (converged, one elected lane), which run asynchronously
+// and report through mbarriers; it is blocked for the length of each product and
+// therefore stages only the first tile, its rows being dealt to ten other warps
+// afterwards.  Warp 0 owns TMEM.
 // TMEM columns: [0,64) S^T, [64,320) the four 128-row slices of O^T.
 //
 // Softmax: running per-head reference max with lazy rescaling (O^T is touched
 // only when a head's max grows by more than 2^8), denominators accumulated per
 // thread and reduced across the 128 rows once, at the end.
 //
+// Two or four splits of a request are launched as one thread-block cluster and
+// merged through distributed shared memory (cluster_merge); other split counts
+// leave normalised partials for the combine kernel.
+//
 // Every mbarrier wait is bounded; a wait that gives up records a code in
-// g_attn_error, and the CTA drains and returns without writing its outputs.
+// g_attn_error, and the CTA walks on without waiting again and drops its outputs.
 #include "attn_params.cuh"
 #include "launchers.h"
 #include "sm100_ptx.cuh"
@@ -58,8 +63,7 @@ constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_S = 0, COL_O = 64;
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 constexpr float RESCALE_THRESHOLD = 8.0f;             // log2 units
-// The thread that issues the MMAs: lane 0 of the last warp, whose share of the K tile is
-// released last by the P.V product, so that the (blocking) issue delays no refill.
+// The warp that issues the MMAs (its lane 0 stamps the debug timeline).
 constexpr int ISSUE_TID = THREADS - 32;
 constexpr int ISSUE_WARP = ISSUE_TID / 32;
 
