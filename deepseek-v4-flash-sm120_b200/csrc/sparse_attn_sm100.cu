@@ -820,7 +820,6 @@ sm100_attn_kernel(const AttnParams p) {
   for (int hh = 0; hh < S::HALVES; ++hh)
     load_half<FMT, DQK, EXTRA>(stage.d[hh], p, lv, lv.begin + geo.row(hh), tidx[hh], geo);
   const ScaleWords sw0 = load_scales(lv.begin + row, ridx);
-  if (n_tiles > 1) prefetch_row(lv.begin + TILE + row, ridx_n1);
 #pragma unroll
   for (int it = 0; it < Q_BATCH; ++it) {
     const int i = tid + it * THREADS;
@@ -834,6 +833,9 @@ sm100_attn_kernel(const AttnParams p) {
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  // The first tile's rows have had HBM to themselves; now, while they are converted, the
+  // second tile's rows are brought into L2.
+  if (n_tiles > 1) prefetch_row(lv.begin + TILE + row, ridx_n1);
   const uint32_t tmem = ctrl.tmem;
   if (tid == 0) stamp(p, 1);
   if (tid == 0) stamp_cta(p, 1);
