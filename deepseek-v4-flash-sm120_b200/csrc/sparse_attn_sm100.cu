@@ -453,9 +453,6 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
 
 // Everything the merge needs, by value (the kernel's parameter block must not have its
 // address taken: that would move it to local memory for the whole kernel).
@@ -492,13 +489,71 @@ __device__ __forceinline__ void stamp_merge(const MergeOut& p, int slot) {
 #endif
 }
 
+// Step (4) of the merge for a cluster of CS CTAs: thread = 4 consecutive d of one head; the
+// loads of BATCH items from all CS sources go out before the first is used (a remote load
+// takes on the order of a microsecond).
+template <int CS, int BATCH>
+__device__ __forceinline__ void pull_slices(const MergeOut& p, const Ctrl& ctrl, const MergeCtx& c,
+                                            float* const (&wtab)[4], uint32_t rank, bool final_out) {
+  constexpr int DL = D_V / CS, QUADS = DL / 4;
+  const int tid = threadIdx.x;
+  const int n_items = c.heads_here * QUADS;
+  __nv_bfloat16* out_base = p.out + c.bi * p.stride_o_b + c.si * p.stride_o_s + c.head0 * p.stride_o_h;
+  for (int item0 = tid; item0 < n_items; item0 += BATCH * THREADS) {
+    float4 v[BATCH][CS];
+#pragma unroll
+    for (int k = 0; k < BATCH; ++k) {
+      const int item = item0 + k * THREADS;
+      const int h = item / QUADS, q = item - h * QUADS;
+      const uint32_t a_loc = c.stage + (h * D_V + rank * DL + 4 * q) * 4;
+#pragma unroll
+      for (int r = 0; r < CS; ++r) {
+        v[k][r] = make_float4(0.f, 0.f, 0.f, 0.f);
+        // weight 0: an empty split, whose memory holds nothing
+        if (item < n_items && wtab[r][h] != 0.f) {
+          if (r == static_cast<int>(rank)) {             // this CTA's own copy: plain shared load
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(v[k][r].x), "=f"(v[k][r].y), "=f"(v[k][r].z), "=f"(v[k][r].w) : "r"(a_loc));
+          } else {
+            const uint32_t a = map_to_rank(a_loc, r);
+            asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(v[k][r].x), "=f"(v[k][r].y), "=f"(v[k][r].z), "=f"(v[k][r].w) : "r"(a));
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < BATCH; ++k) {
+      const int item = item0 + k * THREADS;
+      if (item >= n_items || ctrl.fail) continue;
+      const int h = item / QUADS, q = item - h * QUADS;
+      const int d0 = rank * DL + 4 * q;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int r = 0; r < CS; ++r) {                     // rank order: reproducible sums
+        const float w = wtab[r][h];
+        acc.x = fmaf(w, v[k][r].x, acc.x);
+        acc.y = fmaf(w, v[k][r].y, acc.y);
+        acc.z = fmaf(w, v[k][r].z, acc.z);
+        acc.w = fmaf(w, v[k][r].w, acc.w);
+      }
+      if (final_out) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+        *reinterpret_cast<uint2*>(out_base + h * p.stride_o_h + d0) =
+            make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+      } else {
+        *reinterpret_cast<float4*>(p.o_accum + (c.acc_slot0 + h) * D_V + d0) = acc;
+      }
+    }
+  }
+}
+
 __device__ __noinline__ void cluster_merge(const MergeOut p, Ctrl& ctrl, const MergeCtx c,
                                            float l_own, float m_own) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int cs = p.cluster;                              // 2 or 4
   const uint32_t rank = cluster_rank();
   const bool final_out = p.n_splits == cs;
-  const int dl = D_V / cs;                               // slice width per rank
 
   // (1) own O^T -> own shared memory [head][d]; thread = one d (TMEM lane), 16 heads per load
   if (tid < HEADS) {
@@ -564,56 +619,9 @@ __device__ __noinline__ void cluster_merge(const MergeOut p, Ctrl& ctrl, const M
   __syncthreads();
   stamp_merge(p, 242);
 
-  // (4) pull this rank's slice of every source, 4 consecutive d per thread; the remote
-  // loads of a batch of items all go out before the first is used (their latency is several
-  // hundred nanoseconds)
-  {
-    constexpr int BATCH = 4;
-    const int quads = dl / 4, n_items = c.heads_here * quads;
-    __nv_bfloat16* out_base = p.out + c.bi * p.stride_o_b + c.si * p.stride_o_s + c.head0 * p.stride_o_h;
-    for (int item0 = tid; item0 < n_items; item0 += BATCH * THREADS) {
-      float4 v[BATCH][4];
-#pragma unroll
-      for (int k = 0; k < BATCH; ++k) {
-        const int item = item0 + k * THREADS;
-        const int h = item / quads, q = item - h * quads;
-        const uint32_t a_loc = c.stage + (h * D_V + rank * dl + 4 * q) * 4;
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          v[k][r] = make_float4(0.f, 0.f, 0.f, 0.f);
-          // weight 0: an empty split, whose memory holds nothing
-          if (item < n_items && r < cs && wtab[r][h] != 0.f) {
-            const uint32_t a = map_to_rank(a_loc, r);
-            asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                         : "=f"(v[k][r].x), "=f"(v[k][r].y), "=f"(v[k][r].z), "=f"(v[k][r].w) : "r"(a));
-          }
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < BATCH; ++k) {
-        const int item = item0 + k * THREADS;
-        if (item >= n_items || ctrl.fail) continue;
-        const int h = item / quads, q = item - h * quads;
-        const int d0 = rank * dl + 4 * q;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          const float w = r < cs ? wtab[r][h] : 0.f;
-          acc.x = fmaf(w, v[k][r].x, acc.x);
-          acc.y = fmaf(w, v[k][r].y, acc.y);
-          acc.z = fmaf(w, v[k][r].z, acc.z);
-          acc.w = fmaf(w, v[k][r].w, acc.w);
-        }
-        if (final_out) {
-          __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
-          *reinterpret_cast<uint2*>(out_base + h * p.stride_o_h + d0) =
-              make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-        } else {
-          *reinterpret_cast<float4*>(p.o_accum + (c.acc_slot0 + h) * D_V + d0) = acc;
-        }
-      }
-    }
-  }
+  // (4) pull this rank's slice of every source
+  if (cs == 2) pull_slices<2, 8>(p, ctrl, c, wtab, rank, final_out);
+  else pull_slices<4, 4>(p, ctrl, c, wtab, rank, final_out);
   stamp_merge(p, 243);
   cluster_sync_all();                                    // (5) peers are done reading this CTA
   stamp_merge(p, 244);
