@@ -491,6 +491,26 @@ def run_head_tp(dev, K, ops, W, stream, rank, world, max_over_ranks):
         out[f"{name}_head_tp{world}"] = res
         del wl, call
         torch.cuda.empty_cache()
+
+    # Prefill (configs[4]) sharded by contiguous query blocks of equal pair counts; the KV
+    # workspace is replicated, outputs stay sharded: no exchange.
+    pw = W.config5(dev, ops.kv_store, with_pages=False)
+    lo, hi = sharding.balanced_query_blocks(pw.q.size(0), pw.indices.size(1), world)[rank]
+    q_l, idx_l = pw.q[lo:hi].contiguous(), pw.indices[lo:hi].contiguous()
+    for i in range(2):
+        ops.sparse_prefill_fwd(q_l, pw.kv_bf16, idx_l, pw.sm_scale, 512)
+    dist.barrier()
+    torch.cuda.synchronize(dev)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for i in range(5):
+        ops.sparse_prefill_fwd(q_l, pw.kv_bf16, idx_l, pw.sm_scale, 512)
+    b.record(stream)
+    dist.barrier()
+    torch.cuda.synchronize(dev)
+    ms = max_over_ranks(a.elapsed_time(b)) / 5
+    out[f"cfg5_prefill_query_blocks_x{world}"] = {"ms_per_call": ms, "tflops_total": pw.flops() / (ms * 1e-3) / 1e12,
+                                                 "rows_rank0": hi - lo if rank == 0 else None}
     return out
 
 
@@ -543,6 +563,10 @@ def run_extras(dev, K, ops, W, stream):
     wl = W.config1(dev, ops.kv_store)
     decode_case("cfg1", wl)
     del wl
+    wl = W.config3(dev, ops.kv_store, b=128, n_index_sets=2)     # mixed context lengths, half clustered
+    decode_case("cfg3_b128", wl)
+    del wl
+    torch.cuda.empty_cache()
     wl = W.config4(dev, ops.kv_store)
     call = decode_case("cfg4_128_splits", wl, n_splits=wl.force_splits)
     if call.partial_sets > 1:
@@ -570,6 +594,29 @@ def run_extras(dev, K, ops, W, stream):
     sbytes = pw.q.size(0) * (d_nope * 2 + 128 + 644)      # BF16 in, one 644-byte token out
     out["kv_store_8192_tokens"] = {"us_per_call": ms * 1e3, "gbs": sbytes / (ms * 1e-3) / 1e9,
                                    "frac_of_measured_hbm": sbytes / (ms * 1e-3) / 1e9 / peak}
+
+    # CPU oracle beside it, bounded samples: the single-token case as it is, the long
+    # context on its one request, prefill on one block of 256 query rows (the last rows:
+    # full 2048-entry lists) scaled to the pair count.
+    from oracle import sparse_mla as O
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except Exception:  # noqa: BLE001
+        pass
+    cpu = {"cores": torch.get_num_threads()}
+    for name, wl in (("cfg1", W.config1(dev, ops.kv_store)), ("cfg4", W.config4(dev, ops.kv_store))):
+        t = min(time_cpu_oracle(wl.q.cpu(), wl.kv.cpu(), wl.indices[0].cpu(), wl.sm_scale, 2, 1))
+        cpu[name + "_ms_per_call"] = t * 1e3
+        del wl
+    rows = slice(pw.q.size(0) - 256, pw.q.size(0))
+    q_c, kv_c, idx_c = pw.q[rows].cpu(), pw.kv_bf16.cpu(), pw.indices[rows].cpu()
+    t0 = time.perf_counter()
+    O.sparse_prefill(q_c, kv_c, idx_c, pw.sm_scale, 512)
+    t = time.perf_counter() - t0
+    pairs = int((idx_c >= 0).sum())
+    cpu["cfg5_prefill_tflops"] = pairs * pw.q.size(1) * 2 * (pw.q.size(2) + 512) / t / 1e12
+    cpu["cfg5_sample"] = f"last 256 of {pw.q.size(0)} query rows, {t:.2f} s"
+    out["cpu_oracle"] = cpu
     return out
 
 
