@@ -105,3 +105,38 @@ def test_umma_descriptor_selftest(K, mode, n, k):
         d, status = K.umma_selftest(1, a.t().contiguous().cuda(), b.t().contiguous().cuda())
     assert status == 0, "the MMA never signalled its barrier"
     torch.testing.assert_close(d.cpu(), want, atol=1e-3, rtol=1e-3)
+
+
+def test_head_gather_gives_up_on_a_missing_peer(K):
+    """The peer-memory all-gather waits for every rank's flag with a bound.  Here rank 0
+    of a pretended two-rank group runs alone (the "peer" buffers are local memory and
+    nobody ever sets the peer's flag): the kernel must copy its own shard, give up after
+    its bounded wait, report that through the status word and leave the context usable."""
+    import ctypes as C
+    from deepseek_v4_kernel import _native as N
+    dev = torch.device("cuda", 0)
+    b, h_local, world = 2, 8, 2
+    h_q = h_local * world
+    out_local = torch.randn(b, 1, h_local, 512, device=dev).bfloat16()
+    lse_local = torch.randn(b, h_local, 1, device=dev)
+    gathered = [torch.zeros(b, 1, h_q, 512, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    lse_g = [torch.zeros(b, h_q, 1, device=dev) for _ in range(world)]
+    flags = [torch.zeros(world, dtype=torch.int32, device=dev) for _ in range(world)]
+    counter = torch.zeros(1, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    a = N.GatherArgs()
+    a.world, a.rank, a.b, a.s_q, a.h_local, a.step = world, 0, b, 1, h_local, 1
+    a.out_local, a.lse_local = out_local.data_ptr(), lse_local.data_ptr()
+    for r in range(world):
+        a.peer_out[r], a.peer_lse[r], a.peer_flags[r] = (gathered[r].data_ptr(), lse_g[r].data_ptr(),
+                                                         flags[r].data_ptr())
+    a.counter, a.status = counter.data_ptr(), status.data_ptr()
+    N.check(N.lib.dsv4_gather_heads(C.byref(a), torch.cuda.current_stream().cuda_stream), "gather")
+    torch.cuda.synchronize()
+    assert status.item() == 2                      # 1 + the rank that never arrived
+    assert flags[0][0].item() == 1 and flags[1][0].item() == 1 and flags[0][1].item() == 0
+    for r in range(world):                         # the shard itself did land everywhere
+        assert torch.equal(gathered[r][:, :, :h_local], out_local)
+        assert torch.equal(lse_g[r][:, :h_local], lse_local)
+    # the context is intact: a normal kernel still runs
+    assert torch.equal(out_local + 0, out_local)
