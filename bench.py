@@ -620,6 +620,48 @@ def run_extras(dev, K, ops, W, stream):
     return out
 
 
+def run_prefill(args):
+    """`--workload cfg5[:s_q]`: sparse prefill (configs[4]) on one GPU, one JSON line.
+    The secondary metric of the path (TFLOP/s against the measured BF16 peak); not the line
+    the default run prints."""
+    rank, world, local = dist_env()
+    if rank != 0:
+        return
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    from deepseek_v4_kernel import ops
+    from deepseek_v4_kernel import workloads as W
+    s_q = int(args.workload.split(":")[1]) if ":" in args.workload else 8192
+    pw = W.config5(dev, ops.kv_store, s_q=s_q, with_pages=False)
+    stream = torch.cuda.current_stream(dev)
+    fn = lambda: ops.sparse_prefill_fwd(pw.q, pw.kv_bf16, pw.indices, pw.sm_scale, 512)
+    for _ in range(args.warmup):
+        fn()
+    torch.cuda.synchronize(dev)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(args.steps):
+        fn()
+    b.record(stream)
+    torch.cuda.synchronize(dev)
+    ms = a.elapsed_time(b) / args.steps
+    try:
+        tf_peak = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops_sustained"]
+        src = "measured"
+    except Exception:  # noqa: BLE001
+        tf_peak, src = 1400.0, "fallback"
+    tf = pw.flops() / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "sparse_prefill_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"configs[4]: sparse prefill s_q=s_kv={s_q} h_q=64 causal top-k 2048, BF16 KV workspace",
+                   "pairs": pw.pairs()},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": tf_peak, "unit": "TFLOP/s",
+                     "frac": tf / tf_peak, "traffic": None, "peak_source": src},
+        "gpu_launches": args.steps}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -636,6 +678,8 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload.startswith("cfg5"):
+        run_prefill(args)
     else:
         run_ours(args)
 
