@@ -316,6 +316,32 @@ def run_ours(args):
     peak, peak_src = measured_peaks()
     achieved = mean_bytes / (k_ms * 1e-3) / 1e9
 
+    # ---- (2b) the same calls replayed from a CUDA graph (one graph = one pass over the
+    # index sets), as a serving loop with captured decode steps would issue them
+    graph_us = None
+    try:
+        side = torch.cuda.Stream(dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                for i in range(N_INDEX_SETS):
+                    call.set_indices(wl.indices[i])
+                    call.decode(side.cuda_stream, with_combine=True)
+        torch.cuda.synchronize(dev)
+        reps = max(3, args.steps // N_INDEX_SETS)
+        for _ in range(2):
+            g.replay()
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record(stream)
+        for _ in range(reps):
+            g.replay()
+        g1.record(stream)
+        torch.cuda.synchronize(dev)
+        graph_us = g0.elapsed_time(g1) / (reps * N_INDEX_SETS) * 1e3
+    except Exception as exc:  # noqa: BLE001
+        graph_us = f"unavailable: {exc}"
+
     # ---- (3) end to end through the public operator, host buffers -------------------
     # Every step copies its q and indices from pinned host memory, calls the operator and
     # copies out and lse back to pinned host memory.  As a serving framework does for decode,
@@ -427,6 +453,7 @@ def run_ours(args):
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                     "how": "ops.sparse_decode_fwd with host buffers: upload + operator + download "
                            "captured per index set as a CUDA graph, steps round-robin over 3 streams"},
+            "cuda_graph_us_per_call": graph_us,
             "gpu_launches": args.steps * call.launches_per_call,
             "clocks": clocks.summary(),
         }
