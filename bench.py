@@ -188,7 +188,7 @@ def run_reference(args):
     rank, world, _ = dist_env()
     if rank != 0:
         return
-    from deepseek_v4_kernel import workloads as W
+    import bench_workloads as W
     from oracle import sparse_mla as O
 
     def cpu_quantize(k_nope, k_rope, slots, kv):
@@ -242,7 +242,7 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     from deepseek_v4_kernel import cuda as K
     from deepseek_v4_kernel import ops
-    from deepseek_v4_kernel import workloads as W
+    import bench_workloads as W
 
     params, desc = workload_params(args.workload)
     wl = W.config2(dev, ops.kv_store, n_index_sets=N_INDEX_SETS, seed=rank, **params)
@@ -657,7 +657,7 @@ def run_prefill(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     from deepseek_v4_kernel import ops
-    from deepseek_v4_kernel import workloads as W
+    import bench_workloads as W
     s_q = int(args.workload.split(":")[1]) if ":" in args.workload else 8192
     pw = W.config5(dev, ops.kv_store, s_q=s_q, with_pages=False)
     stream = torch.cuda.current_stream(dev)

@@ -56,12 +56,14 @@ struct AttnParams {
 
 // Effective list lengths of request `req`: `len` entries of the main list then
 // `xlen` of the extra list.  Decode raises a length below one to one, as the
-// reference oracle does (tests/reference.py:108-109); prefill clamps at zero.
+// reference oracle does (tests/reference.py:108-109), unless
+// DSV4_FLAG_ZERO_LENGTH_EMPTY asks for the reference kernel's clamp at zero; prefill
+// clamps at zero.
 __device__ __forceinline__ void request_lengths(const AttnParams& p, int req, int& len, int& xlen) {
   int bi = req / p.s_q;
   len = p.topk;
   if (p.topk_length) len = min(len, p.topk_length[bi]);
-  len = max(len, p.mode == MODE_DECODE ? 1 : 0);
+  len = max(len, (p.mode == MODE_DECODE && !(p.flags & DSV4_FLAG_ZERO_LENGTH_EMPTY)) ? 1 : 0);
   xlen = 0;
   if (p.extra_kv) {
     xlen = p.extra_topk;

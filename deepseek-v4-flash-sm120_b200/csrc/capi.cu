@@ -98,7 +98,7 @@ const char* dsv4_strerror(int s) {
     case DSV4_ERR_CUDA: return "a CUDA runtime call failed";
     case DSV4_ERR_SCRATCH: return "n_splits > 1 needs o_accum and lse_accum";
     case DSV4_ERR_UNSUPPORTED: return "this request is valid but not implemented by this build";
-    case DSV4_ERR_SCRATCH_TOO_LARGE: return "split-KV partials exceed the built-in scratch of dsv4_sparse_decode_noalloc (n_splits * b * s_q * h_q * 512 > DSV4_NOALLOC_MAX_O_FLOATS)";
+    case DSV4_ERR_SCRATCH_TOO_LARGE: return "split-KV partials exceed the built-in scratch of dsv4_sparse_decode_noalloc (partial sets * b * s_q * h_q * 512 > DSV4_NOALLOC_MAX_O_FLOATS)";
     default: return "unknown status";
   }
 }

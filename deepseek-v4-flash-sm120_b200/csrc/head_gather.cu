@@ -69,7 +69,11 @@ gather_heads_kernel(const Dsv4GatherArgs a) {
   __shared__ int s_last;
   if (threadIdx.x == 0) {
     const unsigned int done = atomicAdd(reinterpret_cast<unsigned int*>(a.counter), 1u);
-    s_last = ((done + 1u) % gridDim.x) == 0u;       // the counter is never reset
+    s_last = (done + 1u) == gridDim.x;
+    // The last CTA puts the counter back to zero, so the next call may use another grid
+    // (the grid follows the batch size).  Calls that share a counter are ordered by the
+    // stream, and no CTA of this launch touches the counter after its own increment.
+    if (s_last) *reinterpret_cast<volatile unsigned int*>(a.counter) = 0u;
   }
   __syncthreads();
   if (!s_last) return;

@@ -51,9 +51,12 @@ extern "C" int dsv4_sparse_decode_noalloc(const Dsv4DecodeArgs* args, void* cuda
   Dsv4DecodeArgs a = *args;
   a.o_accum = nullptr;
   a.lse_accum = nullptr;
-  if (a.n_splits > 1) {
+  // Splits that are merged on chip leave no partials: only the sets that really reach the
+  // scratch count against its size.
+  const int sets = a.n_splits > 1 ? dsv4_decode_partial_sets(&a) : 1;
+  if (sets > 1) {
     if (a.b < 0 || a.s_q < 1 || a.h_q < 1) return DSV4_ERR_SHAPE;
-    const long long slots = static_cast<long long>(a.n_splits) * a.b * a.s_q * a.h_q;
+    const long long slots = static_cast<long long>(sets) * a.b * a.s_q * a.h_q;
     if (slots > kMaxLseFloats || slots * 512 > kMaxOFloats) return DSV4_ERR_SCRATCH_TOO_LARGE;
     float* base = nullptr;
     const int rc = scratch_for_current_device(&base);   // first call per device: one-time set-up

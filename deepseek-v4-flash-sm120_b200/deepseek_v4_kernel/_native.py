@@ -13,7 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("DSV4_B200_LIB") or os.path.join(_HERE, "libdsv4_b200.so")
 
 KV_BF16, KV_MODEL1, KV_V32 = 0, 1, 2
-FLAG_MASK_INVALID, FLAG_IMPL_SIMPLE, FLAG_NO_COMBINE = 1, 2, 4
+FLAG_MASK_INVALID, FLAG_IMPL_SIMPLE, FLAG_NO_COMBINE, FLAG_ZERO_LENGTH_EMPTY = 1, 2, 4, 8
 ABI_VERSION = 1
 
 i32, i64, f32, vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p

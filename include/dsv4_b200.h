@@ -55,7 +55,13 @@ enum Dsv4Flags {
   DSV4_FLAG_IMPL_SIMPLE = 2,
   /* Decode with n_splits > 1: stop after writing the partials; the caller runs
    * dsv4_split_combine itself (lets a benchmark time the two kernels apart).           */
-  DSV4_FLAG_NO_COMBINE = 4
+  DSV4_FLAG_NO_COMBINE = 4,
+  /* Decode only: a topk_length below one means "attend to nothing" (out 0, lse = sink
+   * or -inf), as the reference's CUDA kernel treats it
+   * (csrc/sm120/decode/sparse_decode_kernel.cuh:373-375).  Default (flag clear)
+   * follows the reference's torch oracle, which raises such a length to one
+   * (tests/reference.py:108-109).                                                      */
+  DSV4_FLAG_ZERO_LENGTH_EMPTY = 8
 };
 
 /* ---------------------------------------------------------------------------
@@ -67,7 +73,8 @@ enum Dsv4Flags {
  * indices[r, 0:len) of the paged cache (then extra_indices[r, 0:extra_len) of
  * the extra cache when given), V being the first 512 columns of the dequantised
  * row, and writes out[r] (BF16) and lse[r] (fp32, natural log, sink-merged).
- * len = clamp(topk_length[b_idx], 1, topk) when topk_length is given, else topk.
+ * len = clamp(topk_length[b_idx], 1, topk) when topk_length is given, else topk
+ * (lower bound 0 with DSV4_FLAG_ZERO_LENGTH_EMPTY).
  * Strides are in elements of the tensor's own type, except stride_kv_block and
  * stride_extra_kv_block which are in BYTES.  All inner dimensions are dense.
  * q rows and KV pages must be 16-byte aligned.
@@ -129,9 +136,11 @@ int dsv4_sparse_decode(const Dsv4DecodeArgs* args, void* cuda_stream);
  * library until the process exits).  The call performs no cudaMalloc / cudaFree
  * and uses no allocating library routine.
  *
- *  - Limit: n_splits * b * s_q * h_q * 512 <= DSV4_NOALLOC_MAX_O_FLOATS when
- *    n_splits > 1 (batch 16 x 64 heads x 8 splits fits exactly); larger requests
- *    return DSV4_ERR_SCRATCH_TOO_LARGE and launch nothing.
+ *  - Limit: sets * b * s_q * h_q * 512 <= DSV4_NOALLOC_MAX_O_FLOATS, where sets =
+ *    dsv4_decode_partial_sets(args) is the number of partial sets that really
+ *    reach the scratch (splits merged on chip leave none, so n_splits of 2 or 4
+ *    never hit the limit; batch 16 x 64 heads x 8 splits fits exactly); larger
+ *    requests return DSV4_ERR_SCRATCH_TOO_LARGE and launch nothing.
  *  - The FIRST call on each device looks up the array's device address (a cheap,
  *    one-time query with that device current).  Make that first call before any
  *    stream capture begins.

@@ -136,6 +136,31 @@ def test_edge_cases(cuda_mod, flags):
 
 
 @pytest.mark.parametrize("flags", IMPLS)
+@pytest.mark.parametrize("with_sink", [False, True])
+def test_zero_length_attends_to_nothing_on_request(cuda_mod, flags, with_sink):
+    """DSV4_FLAG_ZERO_LENGTH_EMPTY: a topk_length below one gives out 0 and lse = sink or
+    -inf, as the reference's CUDA kernel does (csrc/sm120/decode/sparse_decode_kernel.cuh:
+    373-375, 527-529); the other requests of the batch are unaffected."""
+    ZERO_LENGTH_EMPTY = 8
+    q, pages, idx = fake_batch(3, 16, 4, 200, seed=12)
+    sm = 1 / math.sqrt(512)
+    tk = torch.tensor([0, 150, -3], dtype=torch.int32)
+    sink = torch.randn(16, generator=torch.Generator().manual_seed(3)) if with_sink else None
+    out_ref, lse_ref = O.sparse_decode(q, pages, idx, tk, sink, sm, 64)
+    for n_splits in (1, 2, 3):
+        out, lse = run(cuda_mod, q, pages, idx, sm, tk, sink, flags | ZERO_LENGTH_EMPTY,
+                       n_splits=n_splits)
+        check(out[1:2], lse[1:2], out_ref[1:2], lse_ref[1:2])
+        out, lse = out.cpu(), lse.cpu()
+        for r in (0, 2):
+            assert (out[r] == 0).all()
+            if with_sink:
+                torch.testing.assert_close(lse[r, :, 0], sink)
+            else:
+                assert torch.isneginf(lse[r]).all()
+
+
+@pytest.mark.parametrize("flags", IMPLS)
 def test_multi_query_tokens_and_padded_page_stride(cuda_mod, flags):
     """s_q = 3 (the reference rejects s_q > 1) and a cache whose pages are padded."""
     K = cuda_mod

@@ -140,3 +140,32 @@ def test_head_gather_gives_up_on_a_missing_peer(K):
         assert torch.equal(lse_g[r][:, :h_local], lse_local)
     # the context is intact: a normal kernel still runs
     assert torch.equal(out_local + 0, out_local)
+
+
+def test_head_gather_counter_survives_a_change_of_grid(K):
+    """Two calls that share one counter but differ in batch size (hence in grid): the last
+    CTA of each call must be recognised as such, so every call publishes its flag exactly
+    once, after all of its stores.  One rank, its "peers" being local buffers."""
+    import ctypes as C
+    from deepseek_v4_kernel import _native as N
+    dev = torch.device("cuda", 0)
+    counter = torch.zeros(1, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    flags = torch.zeros(1, dtype=torch.int32, device=dev)
+    step = 0
+    for b in (1, 12, 3, 64, 2):                      # 4, 48, 12, 64 (capped), 8 CTAs
+        step += 1
+        out_local = torch.randn(b, 1, 8, 512, device=dev).bfloat16()
+        lse_local = torch.randn(b, 8, 1, device=dev)
+        gathered = torch.zeros(b, 1, 8, 512, dtype=torch.bfloat16, device=dev)
+        lse_g = torch.zeros(b, 8, 1, device=dev)
+        a = N.GatherArgs()
+        a.world, a.rank, a.b, a.s_q, a.h_local, a.step = 1, 0, b, 1, 8, step
+        a.out_local, a.lse_local = out_local.data_ptr(), lse_local.data_ptr()
+        a.peer_out[0], a.peer_lse[0], a.peer_flags[0] = (gathered.data_ptr(), lse_g.data_ptr(),
+                                                         flags.data_ptr())
+        a.counter, a.status = counter.data_ptr(), status.data_ptr()
+        N.check(N.lib.dsv4_gather_heads(C.byref(a), torch.cuda.current_stream().cuda_stream), "gather")
+        torch.cuda.synchronize()
+        assert status.item() == 0 and flags.item() == step and counter.item() == 0
+        assert torch.equal(gathered, out_local) and torch.equal(lse_g, lse_local)

@@ -33,6 +33,14 @@ def _decode_both_ways(K, N, q, kv4, idx, sm_scale, n_splits):
     assert rc == 0, N.lib.dsv4_strerror(rc).decode()
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated() == before
+    # torch's counter only sees torch's own allocator; the driver's free-memory figure would
+    # also show a cudaMalloc made inside the library.  It is compared from the second call
+    # on (the first call on a device may load the module and resolve the array's address).
+    free_now = torch.cuda.mem_get_info()[0]
+    rc = N.lib.dsv4_sparse_decode_noalloc(C.byref(args), stream)
+    assert rc == 0, N.lib.dsv4_strerror(rc).decode()
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_now
     args.o_accum, args.lse_accum = keep
     assert K.device_status() == 0
     torch.testing.assert_close(call.out.float(), ref_out.float(), atol=5e-3, rtol=5e-3)
@@ -45,7 +53,7 @@ def test_noalloc_decode_matches_regular_entry_twice():
     from deepseek_v4_kernel import _native as N
     from deepseek_v4_kernel import cuda as K
     from deepseek_v4_kernel import ops
-    from deepseek_v4_kernel import workloads as W
+    import bench_workloads as W
 
     dev = torch.device("cuda", 0)
     wl = W.decode_workload("noalloc", b=4, h_q=64, topk=1024, ctx_lens=[4096] * 4, layout="V32",
@@ -53,6 +61,8 @@ def test_noalloc_decode_matches_regular_entry_twice():
     _decode_both_ways(K, N, wl.q, wl.kv, wl.indices[0], wl.sm_scale, n_splits=8)
     # second call: other indices, other split count, scratch still holds call one's partials
     _decode_both_ways(K, N, wl.q, wl.kv, wl.indices[1], wl.sm_scale, n_splits=3)
+    # four splits are merged inside a thread-block cluster: no partials reach the scratch
+    _decode_both_ways(K, N, wl.q, wl.kv, wl.indices[1], wl.sm_scale, n_splits=4)
     # unsplit requests need no scratch and pass straight through
     _decode_both_ways(K, N, wl.q, wl.kv, wl.indices[0], wl.sm_scale, n_splits=1)
 
@@ -64,3 +74,8 @@ def test_noalloc_rejects_oversized_requests():
     rc = N.lib.dsv4_sparse_decode_noalloc(C.byref(a), None)
     assert rc == 9 and b"scratch" in N.lib.dsv4_strerror(rc)
     assert N.lib.dsv4_sparse_decode_noalloc(None, None) == 1
+    # the limit counts the partial sets that reach the scratch: two splits of the same batch
+    # are merged on chip, leave none, and must get past the size check (to the null-pointer
+    # check, since this argument block names no tensors)
+    a.n_splits, a.kv_format, a.d_qk = 2, N.KV_V32, 576
+    assert N.lib.dsv4_sparse_decode_noalloc(C.byref(a), None) == 1
