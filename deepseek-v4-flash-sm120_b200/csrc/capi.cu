@@ -96,7 +96,7 @@ const char* dsv4_strerror(int s) {
     case DSV4_ERR_ALIGN: return "a pointer or stride is not 16-byte aligned";
     case DSV4_ERR_ARCH: return "the current device is not compute capability 10.x (set DSV4_KERNEL_FORCE to override)";
     case DSV4_ERR_CUDA: return "a CUDA runtime call failed";
-    case DSV4_ERR_SCRATCH: return "n_splits > 1 needs o_accum and lse_accum";
+    case DSV4_ERR_SCRATCH: return "this split count leaves partials: o_accum and lse_accum are needed";
     case DSV4_ERR_UNSUPPORTED: return "this request is valid but not implemented by this build";
     case DSV4_ERR_SCRATCH_TOO_LARGE: return "split-KV partials exceed the built-in scratch of dsv4_sparse_decode_noalloc (partial sets * b * s_q * h_q * 512 > DSV4_NOALLOC_MAX_O_FLOATS)";
     default: return "unknown status";
@@ -193,8 +193,11 @@ int dsv4_sparse_decode(const Dsv4DecodeArgs* a, void* stream) {
   if (!aligned16(a->q) || (a->stride_q_b & 7) || (a->stride_q_s & 7) || (a->stride_q_h & 7) ||
       !aligned16(a->out) || (a->stride_o_b & 7) || (a->stride_o_s & 7) || (a->stride_o_h & 7))
     return DSV4_ERR_ALIGN;
-  if (a->n_splits > 1 && (!a->o_accum || !a->lse_accum)) return DSV4_ERR_SCRATCH;
-  if (a->n_splits > 1 && !aligned16(a->o_accum)) return DSV4_ERR_ALIGN;
+  // Scratch is needed only when partials really leave the chip (see dsv4_decode_partial_sets).
+  if (dsv4_decode_partial_sets(a) > 1) {
+    if (!a->o_accum || !a->lse_accum) return DSV4_ERR_SCRATCH;
+    if (!aligned16(a->o_accum)) return DSV4_ERR_ALIGN;
+  }
   if ((rc = current_device_is_sm100())) return rc;
   if (a->b == 0) return DSV4_OK;
 

@@ -1,44 +1,54 @@
 // Sparse MLA attention on the 5th-generation tensor cores (tcgen05 + TMEM).
 //
-// One CTA handles one (request, block of <= 64 heads, split) and walks the
+// One CTA handles one (request, block of NH <= 64 heads, split) and walks the
 // request's index list in tiles of 128 entries.  Gathered KV rows are the M
-// dimension of the MMAs ("tokens as M"), heads are N = 64:
+// dimension of the MMAs ("tokens as M"), heads are N = NH (16, 32 or 64):
 //
-//   S^T[128 tok, 64 heads]  = K[128 tok, d_qk]      . Q^T      (K-major A and B)
-//   O^T[512 d_v, 64 heads] += V^T[512, 128 tok]     . P^T      (MN-major A and B)
+//   S^T[128 tok, NH heads]  = K[128 tok, d_qk]      . Q^T      (K-major A and B)
+//   O^T[512 d_v, NH heads] += V^T[512, 128 tok]     . P^T      (MN-major A and B)
 //
 // V is the first 512 columns of the same dequantised K tile, so ONE shared-
 // memory tile serves both products: it is stored as d_qk/64 blocks of
 // [128 tokens][64 values] with the 128-byte swizzle, which reads as K-major
 // (contraction over d) for the first product and as MN-major (contraction over
 // tokens) for the second.  With d_qk = 576 the tile (144 KB) and Q (72 KB) leave
-// no room for a second tile or a staging ring, so gathered rows are staged in
-// REGISTERS: a tile is 8 "k-steps" of 16 rows; every warp owns four rows of two
-// k-steps, issues their 16-byte loads a tile ahead, and converts and writes them
-// (dequantised to BF16) as soon as the P.V MMA step that last read those rows has
-// retired.  P^T (16 KB) reuses the RoPE block of the tile, which only Q.K^T
-// reads, when d_qk = 576.
+// no room for a second tile, so the tile is recycled BLOCK BY BLOCK:
 //
-// All 16 warps are alike (512 threads x 128 registers = the whole register
-// file) and move through the phases of a tile together: softmax of S^T (thread
-// = one tile row = one TMEM lane, 16 of the 64 heads) -> refill the K tile behind
-// the P.V product and reload the registers for the tile after.  The last warp
-// also issues the MMAs (converged, one elected lane), which run asynchronously
-// and report through mbarriers; it is blocked for the length of each product and
-// therefore stages only the first tile, its rows being dealt to ten other warps
-// afterwards.  Warp 0 owns TMEM.
-// TMEM columns: [0,64) S^T, [64,320) the four 128-row slices of O^T.
+//   * P.V runs slice-major: the eight k-steps of output slice 0 (d 0..127, tile
+//     blocks 0 and 1), then slice 1, ... each followed by a tcgen05.commit.  When
+//     slice g retires, blocks 2g and 2g+1 are dead and the worker warps write the
+//     same blocks of the NEXT tile over them (group g of the refill);
+//   * Q.K^T of the next tile is issued block by block behind the refill, each
+//     group of blocks waiting on its own mbarrier, so the tensor pipe goes from
+//     P.V(t) straight into Q.K^T(t+1) and only idles while softmax(t+1) runs.
 //
-// Softmax: running per-head reference max with lazy rescaling (O^T is touched
-// only when a head's max grows by more than 2^8), denominators accumulated per
-// thread and reduced across the 128 rows once, at the end.
+// Gathered FP8 rows are staged in REGISTERS a tile ahead (16 worker warps x 128-byte
+// lines: 80 KB in flight per SM): a worker owns two rows of the tile; when a group
+// is free it converts and stores the matching 128-byte line of its rows and at once
+// re-issues the loads of the same line of the tile after.  Flat BF16 rows (prefill
+// workspace) need no conversion and go from global to shared memory with cp.async.
+//
+// Warps: 16 workers (gather, convert, softmax, epilogue) and one warp that only issues
+// MMAs (converged, one elected lane).  TMEM columns: [0, NH) S^T, [64 + 64 mb, +NH) the
+// four 128-row slices of O^T.
+//
+// Softmax: per-head reference maximum with lazy rescaling.  A tile is first evaluated
+// against the reference as it stands; only if some logit exceeds it by more than 2^8
+// (always on the first tile) do the workers meet, raise the reference and rescale O^T.
+// The common tile costs one named barrier (an OR over the workers) and no reduction;
+// denominators are accumulated per thread and reduced across the 128 rows once, at the end.
 //
 // Two or four splits of a request are launched as one thread-block cluster and
 // merged through distributed shared memory (cluster_merge); other split counts
 // leave normalised partials for the combine kernel.
 //
 // Every mbarrier wait is bounded; a wait that gives up records a code in
-// g_attn_error, and the CTA walks on without waiting again and drops its outputs.
+// g_attn_error, and the CTA walks on without waiting again, drops its outputs and
+// writes NaN into the log-sum-exp slots it owns so that the failure is visible
+// downstream without a host synchronisation.
+#include <mutex>
+#include <type_traits>
+
 #include "attn_params.cuh"
 #include "launchers.h"
 #include "sm100_ptx.cuh"
@@ -52,55 +62,75 @@ namespace {
 using namespace ptx;
 
 constexpr int TILE = 128;              // index entries per tile (= MMA M)
-constexpr int HEADS = 64;              // heads per CTA (= MMA N)
-constexpr int WARPS = 16;
-constexpr int THREADS = WARPS * 32;    // 512 threads x 128 registers
+constexpr int MAX_HEADS = 64;          // most heads per CTA (= largest MMA N)
+constexpr int WORKER_WARPS = 16;
+constexpr int WORKERS = WORKER_WARPS * 32;
+// A fifth warpgroup holds the warp that only issues MMAs (its other three warps idle at
+// the CTA barriers).  It gives most of its registers back (setmaxnreg), which is what lets
+// the 16 worker warps, four per scheduler, have 112 registers each: a 17th full-size warp
+// would cap every thread at 96.
+constexpr int THREADS = WORKERS + 128;
+constexpr int ISSUE_WARP = WORKER_WARPS;
+// Registers move between warpgroups inside the CTA's own allocation (640 threads x 96 at
+// launch): 512 x 112 + 128 x 32 uses it up exactly.  Asking for more would block for ever.
+constexpr int LAUNCH_REGS = 96, WORKER_REGS = 112, ISSUER_REGS = 32;
+static_assert(WORKERS * WORKER_REGS + (THREADS - WORKERS) * ISSUER_REGS <= THREADS * LAUNCH_REGS,
+              "setmaxnreg.inc can only take what setmaxnreg.dec gave back");
+static_assert(THREADS * (LAUNCH_REGS + 8) > 65536, "LAUNCH_REGS is what the launch bound yields");
 constexpr int KSTEPS = TILE / 16;      // P.V contraction steps per tile
-constexpr int COLS_PER_WARP = HEADS / (WARPS / 4);    // 16 head columns per softmax thread
 constexpr int KBLOCK_BYTES = TILE * 128;              // [128 tok][64 bf16]
-constexpr int QBLOCK_BYTES = HEADS * 128;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t COL_S = 0, COL_O = 64;
+constexpr uint32_t COL_S = 0, COL_O = 64, O_SLICE_COLS = 64;
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 constexpr float RESCALE_THRESHOLD = 8.0f;             // log2 units
-// The warp that issues the MMAs (its lane 0 stamps the debug timeline).
-constexpr int ISSUE_TID = THREADS - 32;
-constexpr int ISSUE_WARP = ISSUE_TID / 32;
+constexpr float NEG_HUGE = -3.0e38f;                  // "no reference maximum yet"
+constexpr int WORKER_BARRIER = 1;                     // named barrier of the 512 workers
 
-enum ErrCode { ERR_KFULL = 1, ERR_PFULL = 2, ERR_SFULL = 3, ERR_KVFREE = 4, ERR_ODONE = 5 };
+enum ErrCode { ERR_BLKFULL = 1, ERR_PFULL = 2, ERR_SFULL = 3, ERR_SLICEFREE = 4, ERR_ODONE = 5 };
 
-template <int FMT, int DQK> struct Cfg {
+template <int FMT, int DQK, int NH> struct Cfg {
+  static_assert(NH == 16 || NH == 32 || NH == 64, "heads per CTA");
   static constexpr bool PAGED = FMT != DSV4_KV_BF16;
   static constexpr int NB = DQK / 64;                  // 64-wide blocks of the K tile
+  static constexpr int NG = NB == 9 ? 5 : 4;           // refill groups: block pairs, then block 8
   static constexpr int NOPE_SEGS = PAGED ? (DQK - 64) / 64 : 0;   // 64-byte FP8 segments
   static constexpr bool P_ALIAS = (DQK == 576);        // P^T lives in the last block
   static constexpr int K_BYTES = NB * KBLOCK_BYTES;
+  static constexpr int QBLOCK_BYTES = NH * 128;
   static constexpr int Q_BYTES = NB * QBLOCK_BYTES;
-  static constexpr int P_BYTES = P_ALIAS ? 0 : TILE * 128;
-  // words per tile row in the multiplier table: a (first, second) factor pair per scale
-  // byte; V32 has 4 scale bytes, MODEL1 7 (padded to 8)
-  static constexpr int MUL_PER_ROW = !PAGED ? 0 : (DQK == 576 ? 8 : 16);
-  static constexpr int MUL_TAB_BYTES = 2 * TILE * MUL_PER_ROW * 4;      // double-buffered
+  static constexpr int P_ROW_BYTES = NH * 2;
+  static constexpr int P_BYTES = P_ALIAS ? 0 : TILE * P_ROW_BYTES;
+  static constexpr int CPW = NH / 4;                   // head columns per softmax thread
+  static constexpr uint32_t P_SWIZZLE = NH == 64 ? SWZ_128B : NH == 32 ? SWZ_64B : SWZ_32B;
 };
 
 struct Ctrl {
-  uint64_t k_full, s_full, p_full, o_done;
-  uint64_t kv_free[KSTEPS];            // one per P.V k-step (16 tile rows)
+  uint64_t blk_full[5];                // group g of the K tile is in shared memory
+  uint64_t slice_free[4];              // P.V slice mb has retired (blocks 2mb, 2mb+1 are dead)
+  uint64_t s_full, p_full, o_done;
   uint32_t tmem;
-  int resc[2];
+  int resc;
   int fail;
-  alignas(16) float wred[4][HEADS];    // per-lane-group column partials (max, then sums)
-  alignas(16) float mref[HEADS];       // reference max, log2-scaled units (read as float4)
-  float mtrue[HEADS];                  // true running max, log2-scaled units
-  float alpha[HEADS];                  // rescale factor / final output factor
+  int pad;
+  alignas(16) float wred[4][MAX_HEADS];  // per-lane-group column partials (max, then sums)
+  alignas(16) float mref[MAX_HEADS];     // reference max, log2-scaled units (read as float4)
+  float alpha[MAX_HEADS];                // rescale factor / final output factor
+  float aux[MAX_HEADS];                  // fourth weight table of the cluster merge
+  float wmax[4][MAX_HEADS];              // per-lane-group column maxima of the raw scores (prefill)
 };
 
-static_assert(sizeof(Ctrl) % 16 == 0, "the multiplier table behind Ctrl is read as uint4");
-
-template <int FMT, int DQK>
+template <int FMT, int DQK, int NH>
 constexpr size_t smem_bytes() {
-  using C = Cfg<FMT, DQK>;
-  return 1024 + C::K_BYTES + C::Q_BYTES + C::P_BYTES + sizeof(Ctrl) + C::MUL_TAB_BYTES;
+  using C = Cfg<FMT, DQK, NH>;
+  return 1024 + C::K_BYTES + C::Q_BYTES + C::P_BYTES + sizeof(Ctrl);
+}
+
+template <int I, int N, class F>
+__device__ __forceinline__ void static_for(F&& f) {
+  if constexpr (I < N) {
+    f(std::integral_constant<int, I>{});
+    static_for<I + 1, N>(f);
+  }
 }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -116,47 +146,23 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c),
                "r"(d));
 }
+__device__ __forceinline__ void st_shared_v2(uint32_t addr, uint32_t a, uint32_t b) {
+  asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b));
+}
 
 // 16 bytes of a KV row.  The rows are read once, so they are not kept in L1 (its array is
 // the one the tensor core reads its operands from).
 __device__ __forceinline__ uint4 ldg16(const uint8_t* p) {
   uint4 v;
-#ifdef DSV4_LDG_ALLOCATE
-  v = __ldg(reinterpret_cast<const uint4*>(p));
-#else
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-#endif
   return v;
 }
 
-__device__ __forceinline__ uint32_t ldg_u32(const uint32_t* p) {
+__device__ __forceinline__ uint32_t ldg_u32(const uint8_t* p) {
   uint32_t v;
   asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
   return v;
-}
-
-// Column-wise reduction, over the 32 lanes of a warp, of a 16-column slice held
-// one row per lane: afterwards v[0] of lane l is the reduction of column l & 15.
-template <bool IS_MAX>
-__device__ __forceinline__ float warp_col_reduce16(float (&v)[16], int lane) {
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const float got = __shfl_xor_sync(0xffffffffu, v[i], 16);
-    v[i] = IS_MAX ? fmaxf(v[i], got) : v[i] + got;
-  }
-#pragma unroll
-  for (int w = 8; w >= 1; w >>= 1) {
-    const bool up = (lane & w) != 0;
-#pragma unroll
-    for (int i = 0; i < w; ++i) {
-      const float mine = up ? v[w + i] : v[i];
-      const float other = up ? v[i] : v[w + i];
-      const float got = __shfl_xor_sync(0xffffffffu, other, w);
-      v[i] = IS_MAX ? fmaxf(mine, got) : mine + got;
-    }
-  }
-  return v[0];
 }
 
 __device__ __forceinline__ uint32_t bf16x2_max(uint32_t a, uint32_t b) {
@@ -164,22 +170,24 @@ __device__ __forceinline__ uint32_t bf16x2_max(uint32_t a, uint32_t b) {
   asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
 
-// Column-wise maximum, over the 32 lanes of a warp, of 16 columns held one row per lane.
-// Values are rounded to BF16 first (packed pairs halve the shuffles); the result only
-// serves as the softmax reference point, which needs to be the same for every thread,
-// not exact.  Lane l returns the maximum of column l & 15.
-__device__ __forceinline__ float warp_col_max16_bf16(const float (&v)[16], int lane) {
-  uint32_t pk[8];
+// Column-wise maximum, over the 32 lanes of a warp, of N columns held one row per lane as
+// N/2 packed BF16 pairs (column 2i in the low half of pk[i]).  Lane l returns the maximum
+// of column l & (N - 1).  The array is used as scratch.
+template <int N>
+__device__ __forceinline__ float warp_col_max_packed(uint32_t (&pk)[N / 2], int lane) {
+  constexpr int NP = N / 2;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-    pk[i] = *reinterpret_cast<uint32_t*>(&t);
+  for (int d = 16; d >= 2 * NP; d >>= 1) {      // lanes further apart than the columns: plain max
+#pragma unroll
+    for (int i = 0; i < NP; ++i) pk[i] = bf16x2_max(pk[i], __shfl_xor_sync(0xffffffffu, pk[i], d));
   }
 #pragma unroll
-  for (int i = 0; i < 8; ++i) pk[i] = bf16x2_max(pk[i], __shfl_xor_sync(0xffffffffu, pk[i], 16));
-#pragma unroll
-  for (int w = 4; w >= 1; w >>= 1) {            // lanes 8, 4, 2 apart: halve the register set
+  for (int w = NP / 2; w >= 1; w >>= 1) {       // lanes 2w apart: halve the register set
     const bool up = (lane & (2 * w)) != 0;
 #pragma unroll
     for (int i = 0; i < w; ++i) {
@@ -192,6 +200,28 @@ __device__ __forceinline__ float warp_col_max16_bf16(const float (&v)[16], int l
   return __uint_as_float((lane & 1) ? (r & 0xffff0000u) : (r << 16));
 }
 
+// Column-wise sum, over the 32 lanes of a warp, of N columns held one row per lane:
+// afterwards v[0] of lane l is the sum of column l & (N - 1).
+template <int N>
+__device__ __forceinline__ float warp_col_sum(float (&v)[N], int lane) {
+#pragma unroll
+  for (int d = 16; d >= N; d >>= 1) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], d);
+  }
+#pragma unroll
+  for (int w = N / 2; w >= 1; w >>= 1) {
+    const bool up = (lane & w) != 0;
+#pragma unroll
+    for (int i = 0; i < w; ++i) {
+      const float mine = up ? v[w + i] : v[i];
+      const float other = up ? v[i] : v[w + i];
+      v[i] = mine + __shfl_xor_sync(0xffffffffu, other, w);
+    }
+  }
+  return v[0];
+}
+
 // Debug timeline: SM cycle counter of CTA (0,0,0) into p.prof[slot] when a buffer is set.
 // Compiled in only with -DDSV4_TIMELINE (the stamps cost instructions in the hot loop).
 __device__ __forceinline__ void stamp(const AttnParams& p, int slot) {
@@ -202,7 +232,7 @@ __device__ __forceinline__ void stamp(const AttnParams& p, int slot) {
   (void)slot;
 #endif
 }
-constexpr int PROF_TILE0 = 8, PROF_PER_TILE = 8, PROF_MAX_TILES = 15;
+constexpr int PROF_TILE0 = 8, PROF_PER_TILE = 8, PROF_MAX_TILES = 24;
 // Per-CTA wall-clock stamps (global timer, ns) at slots 256 + 4 * cta + k; the buffer holds
 // 256 + 4 * CTAs values.
 __device__ __forceinline__ void stamp_cta(const AttnParams& p, int k) {
@@ -238,35 +268,36 @@ __device__ __forceinline__ int list_index(const ListView& lv, int j) {
 }
 
 // ---------------------------------------------------------------------------
-// Register staging of one tile.  A tile is 8 "k-steps" of 16 rows (the rows one
-// P.V MMA step contracts over).  Warp w owns, in the two k-steps j = (w >> 2) and
-// j = 4 + (w >> 2), the four rows 4 * (w & 3) .. +4: lane l holds, for each
-// 128-byte line c of a row, one 16-byte chunk of row (l & 1) + 2 (l >> 4).  The eight
-// lanes that a 128-bit shared-memory store handles together thus belong to two rows whose
-// swizzle patterns differ in the lowest bit, and the chunk a lane takes within a line is
-// chosen (differently for converted and for copied lines) so that those eight lanes hit
-// eight different 16-byte bank groups: no store is replayed.
-// A warp-wide load touches four cache lines, the line number is a
-// compile-time constant of every load/convert/store (addresses reduce to a
-// per-thread base plus an immediate), and a warp needs two list entries and two
-// waits per tile.  When P.V retires k-step j the four warps owning it refill it;
-// the owners of different k-steps sit on different schedulers.
+// Staging geometry.  A tile is 8 "k-steps" of 16 rows (the rows one P.V MMA step
+// contracts over).  Worker warp w owns, in the k-steps j = (w >> 2) and 4 + (w >> 2),
+// the four rows 4 * (w & 3) .. +4, i.e. a thread owns two rows 64 apart: lane l holds,
+// for each 128-byte line c of a row, one 16-byte chunk of row (l & 1) + 2 (l >> 4).  The
+// eight lanes that a 128-bit shared-memory store handles together thus belong to two
+// rows whose swizzle patterns differ in the lowest bit, and the chunk a lane takes
+// within a line is chosen (differently for converted and for copied lines) so that those
+// eight lanes hit eight different 16-byte bank groups: no store is replayed.
 //   paged layouts: a row is CH 16-byte chunks: FP8 chunks (16 values -> two BF16
 //                  chunks of block chunk/4) then 8 RoPE chunks (copied to the last block);
-//   flat BF16:     a row is d_qk/8 chunks copied as they are; rows are twice as wide,
-//                  so the two k-steps are staged one after the other.
-// Scale factors come from a per-tile table in shared memory (one load per row).
+//                  line c < 4 of the FP8 part is exactly the pair of blocks 2c, 2c+1;
+//   flat BF16:     a row is d_qk/8 chunks copied as they are; line c is block c.
 // ---------------------------------------------------------------------------
 template <int FMT, int DQK> struct Stage {
-  using C = Cfg<FMT, DQK>;
-  static constexpr int CH = C::PAGED ? C::NOPE_SEGS * 4 + 8 : DQK / 8;   // 16-byte chunks per row
-  static constexpr int FP8_CH = C::PAGED ? C::NOPE_SEGS * 4 : 0;
+  static constexpr bool PAGED = FMT != DSV4_KV_BF16;
+  static constexpr int NOPE_SEGS = PAGED ? (DQK - 64) / 64 : 0;
+  static constexpr int CH = PAGED ? NOPE_SEGS * 4 + 8 : DQK / 8;   // 16-byte chunks per row
+  static constexpr int FP8_CH = PAGED ? NOPE_SEGS * 4 : 0;
   static constexpr int LINES = (CH + 7) / 8;
-  static constexpr int PHASES = C::PAGED ? 1 : 2;
-  static constexpr int HALVES = 2 / PHASES;                // k-steps held in registers at once
+  static constexpr int REG_LINES = PAGED ? LINES : 1;              // BF16 rows are not staged
   // Line c holds no FP8 chunk (it is copied, not converted).
   __host__ __device__ static constexpr bool copied_line(int c) { return 8 * c >= FP8_CH; }
-  uint4 d[HALVES][LINES];
+  // Lines of refill group g: [first, last].
+  __host__ __device__ static constexpr int first_line(int g, int ng) {
+    return PAGED ? g : 2 * g;
+  }
+  __host__ __device__ static constexpr int last_line(int g, int ng) {
+    return PAGED ? (g == ng - 1 ? LINES - 1 : g) : (2 * g + 1 < LINES ? 2 * g + 1 : LINES - 1);
+  }
+  uint4 d[2][REG_LINES];
 };
 
 // Per-thread constants of the staging geometry.
@@ -275,7 +306,7 @@ struct Geo {
   int rloc;     // row within a k-step: 4 * (w & 3) + (l & 1) + 2 * (l >> 4)
   int piece;    // 16-byte chunk within a converted (FP8) line; it is stored as two chunks
   int piece_cp; // 16-byte chunk within a line that is copied as it is
-  __device__ __forceinline__ int row(int jhalf) const { return 16 * (4 * jhalf + jsub) + rloc; }
+  __device__ __forceinline__ int row(int hh) const { return 16 * (4 * hh + jsub) + rloc; }
 };
 
 // Cache geometry of list entry j (main or extra cache).
@@ -307,111 +338,120 @@ __device__ __forceinline__ const uint8_t* row_ptr(const CacheSel& c, int idx, co
     const int page = c.sh >= 0 ? (idx >> c.sh) : (idx / c.pb);
     const int rr = idx - page * c.pb;
     const uint8_t* pbase = c.kv + static_cast<int64_t>(page) * c.stride;
-    scl = pbase + c.pb * T::ROW_BYTES + rr * T::SLOTS;
-    return pbase + rr * T::ROW_BYTES;
+    scl = pbase + static_cast<int64_t>(c.pb) * T::ROW_BYTES + rr * T::SLOTS;
+    return pbase + static_cast<int64_t>(rr) * T::ROW_BYTES;
   }
 }
 
-// Issue the loads of this lane's row of k-step 4 * jhalf + jsub (list entry j, token
-// idx) into one register set.
-template <int FMT, int DQK, bool EXTRA>
-__device__ __forceinline__ void load_half(uint4 (&d)[Stage<FMT, DQK>::LINES], const AttnParams& p,
-                                          const ListView& lv, int j, int idx, const Geo& geo) {
-  using S = Stage<FMT, DQK>;
+// The UE8M0 scale bytes of one row, as loaded (one or two 32-bit words).
+template <int FMT> struct ScaleWords {
+  static constexpr int N = FMT == DSV4_KV_MODEL1 ? 2 : 1;
+  uint32_t w[N];
+};
+constexpr uint32_t NEUTRAL_SCALES = 0x7f7f7f7fu;       // 2^0 in every byte
+
+// A word holds a scale byte that one packed multiply cannot apply: 0 or above 134.
+__device__ __forceinline__ bool has_rare_scale(uint32_t w) {
+  return __vcmpeq4(w, 0u) != 0u || __vcmpgtu4(w, 0x86868686u) != 0u;
+}
+
+// Row pointer and scale words of list entry (j, idx).
+template <int FMT, bool EXTRA>
+__device__ __forceinline__ const uint8_t* resolve_row(const AttnParams& p, const ListView& lv, int j,
+                                                      int idx, ScaleWords<FMT>& sw) {
   const uint8_t* scl;
   const uint8_t* row = row_ptr<FMT>(cache_of<EXTRA>(p, lv, j), idx, scl);
-  if (row == nullptr) {                  // the entry names no row: a row of zeros
 #pragma unroll
-    for (int c = 0; c < S::LINES; ++c) d[c] = make_uint4(0, 0, 0, 0);
-    return;
-  }
+  for (int k = 0; k < ScaleWords<FMT>::N; ++k) sw.w[k] = NEUTRAL_SCALES;
+  if constexpr (FMT != DSV4_KV_BF16) {
+    if (row != nullptr) {
 #pragma unroll
-  for (int c = 0; c < S::LINES; ++c) {
-    const int piece = S::copied_line(c) ? geo.piece_cp : geo.piece;
-    if constexpr (8 * (S::LINES - 1) + 7 < S::CH) {
-      d[c] = ldg16(row + 16 * piece + 128 * c);       // every line is full
-    } else {
-      d[c] = make_uint4(0, 0, 0, 0);
-      if (8 * c + 7 < S::CH || 8 * c + piece < S::CH) d[c] = ldg16(row + 16 * piece + 128 * c);
+      for (int k = 0; k < ScaleWords<FMT>::N; ++k) sw.w[k] = ldg_u32(scl + 4 * k);
+      // the eighth slot of the 584-byte layout is padding, not a scale
+      if constexpr (FMT == DSV4_KV_MODEL1) sw.w[1] = (sw.w[1] & 0x00ffffffu) | 0x7f000000u;
     }
   }
+  return row;
 }
 
-// One line of a row only (line number known at run time; warp-uniform).
-template <int FMT, int DQK, bool EXTRA>
-__device__ __forceinline__ void load_one_line(uint4& d, int line, const AttnParams& p,
-                                              const ListView& lv, int j, int idx, const Geo& geo) {
-  using S = Stage<FMT, DQK>;
-  const uint8_t* scl;
-  const uint8_t* row = row_ptr<FMT>(cache_of<EXTRA>(p, lv, j), idx, scl);
-  const int piece = S::copied_line(line) ? geo.piece_cp : geo.piece;
-  d = make_uint4(0, 0, 0, 0);
-  if (row != nullptr && 8 * line + piece < S::CH) d = ldg16(row + 16 * piece + 128 * line);
-}
-
-// Convert and store line LINE of the staged row `v` (tile row `row`).  `mul_row` holds the
-// row's entries of the multiplier table: per scale byte s a pair of packed-BF16 factors,
-// (2^(s-7), 1) normally, (2^120, 2^(s-127)) for s = 0 or s > 134.  Both multiplies are always
-// done (the second is exact either way): straight-line code beats a branch per line here.
+// Issue the load of this lane's chunk of line LINE of `row` (null: zeros).
 template <int FMT, int DQK, int LINE>
-__device__ __forceinline__ void store_line(const uint4& v, uint32_t sK, int row, const Geo& geo,
-                                           const uint32_t (&mul_row)[Cfg<FMT, DQK>::MUL_PER_ROW + 2]) {
+__device__ __forceinline__ void load_line(uint4& d, const uint8_t* row, const Geo& geo) {
   using S = Stage<FMT, DQK>;
-  using C = Cfg<FMT, DQK>;
+  const int piece = S::copied_line(LINE) ? geo.piece_cp : geo.piece;
+  d = make_uint4(0, 0, 0, 0);
+  if (row != nullptr && (8 * LINE + 7 < S::CH || 8 * LINE + piece < S::CH))
+    d = ldg16(row + 16 * piece + 128 * LINE);
+}
+
+// e4m3 -> BF16 with the block scale, two values per packed multiply.  The byte, sign-
+// extended to 16 bits and shifted left by four, has the e4m3 magnitude bits where a BF16
+// word reads them as value * 2^-120 (normals and subnormals alike) and the sign in bit 15;
+// c1 = 2^(s - 7) in both halves then rescales and applies the UE8M0 scale in one exact
+// multiply (the product has at most four significant bits).
+// (prmt through inline PTX: __byte_perm drops the selector bit that asks for the sign.)
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+__device__ __forceinline__ void dequant4(uint32_t w, uint32_t c1, uint32_t& lo, uint32_t& hi) {
+  const uint32_t t0 = prmt(w, 0u, 0x9180u);           // [b0, sign(b0), b1, sign(b1)]
+  const uint32_t t1 = prmt(w, 0u, 0xB3A2u);           // [b2, sign(b2), b3, sign(b3)]
+  lo = bf16x2_mul((t0 << 4) & 0x87F087F0u, c1);
+  hi = bf16x2_mul((t1 << 4) & 0x87F087F0u, c1);
+}
+
+// Scale byte that applies to this lane's FP8 chunk of line LINE.
+template <int FMT, int LINE>
+__device__ __forceinline__ uint32_t scale_byte_of(const ScaleWords<FMT>& sw, int piece) {
+  if constexpr (FMT == DSV4_KV_V32) {                 // one scale per 128 values = per line
+    return (sw.w[0] >> ((8 * LINE) & 31)) & 0xffu;
+  } else {                                            // one per 64 values = per half line
+    return __byte_perm(sw.w[0], sw.w[1], 2 * LINE + (piece >> 2)) & 0xffu;
+  }
+}
+
+// Convert and store line LINE of the staged row `v` (tile row `row`).  RARE selects the
+// two-multiply form that also covers scale bytes 0 and above 134.
+template <int FMT, int DQK, int LINE, bool RARE>
+__device__ __forceinline__ void store_line(const uint4& v, uint32_t sK, int row, const Geo& geo,
+                                           const ScaleWords<FMT>& sw) {
+  using S = Stage<FMT, DQK>;
+  constexpr int NB = DQK / 64;
   const int piece = S::copied_line(LINE) ? geo.piece_cp : geo.piece;
   const int x = row & 7;
   const uint32_t rbase = sK + row * 128;
   const int ci = 8 * LINE + piece;
-  if constexpr (C::PAGED) {
-    using T = KvTraits<FMT>;
+  if constexpr (S::PAGED) {
     constexpr bool ALL_FP8 = 8 * LINE + 7 < S::FP8_CH, NO_FP8 = 8 * LINE >= S::FP8_CH;
     if (ALL_FP8 || (!NO_FP8 && ci < S::FP8_CH)) {
-      uint32_t c1, c2;
-      if constexpr (T::TILE == 128) {                           // 8 chunks per scale tile
-        c1 = mul_row[2 * LINE];
-        c2 = mul_row[2 * LINE + 1];
-      } else {                                                  // 4 chunks per scale tile
-        c1 = (piece & 4) ? mul_row[4 * LINE + 2] : mul_row[4 * LINE];
-        c2 = (piece & 4) ? mul_row[4 * LINE + 3] : mul_row[4 * LINE + 1];
-      }
+      const uint32_t s = scale_byte_of<FMT, LINE>(sw, piece);
       uint32_t o[8];
-      dequant4_one_mul(v.x, c1, o[0], o[1]);
-      dequant4_one_mul(v.y, c1, o[2], o[3]);
-      dequant4_one_mul(v.z, c1, o[4], o[5]);
-      dequant4_one_mul(v.w, c1, o[6], o[7]);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) o[k] = bf16x2_mul(o[k], c2);  // 1.0 except for rare scale bytes
+      if constexpr (!RARE) {
+        const uint32_t c1 = (s + 120u) * 0x00800080u;             // packed BF16 2^(s-7)
+        dequant4(v.x, c1, o[0], o[1]);
+        dequant4(v.y, c1, o[2], o[3]);
+        dequant4(v.z, c1, o[4], o[5]);
+        dequant4(v.w, c1, o[6], o[7]);
+      } else {
+        const ScaleMul m = make_scale_mul(s);
+        dequant4_fast(v.x, m, o[0], o[1]);
+        dequant4_fast(v.y, m, o[2], o[3]);
+        dequant4_fast(v.z, m, o[4], o[5]);
+        dequant4_fast(v.w, m, o[6], o[7]);
+      }
       const uint32_t a = rbase + (ci >> 2) * KBLOCK_BYTES + (((2 * (ci & 3)) ^ x) << 4);
       st_shared_v4(a, o[0], o[1], o[2], o[3]);
       st_shared_v4(a ^ 16, o[4], o[5], o[6], o[7]);             // the neighbouring chunk
     } else if (ci < S::CH) {
-      const uint32_t a = rbase + (C::NB - 1) * KBLOCK_BYTES;
+      const uint32_t a = rbase + (NB - 1) * KBLOCK_BYTES;
       st_shared_v4(a + (((ci - S::FP8_CH) ^ x) << 4), v.x, v.y, v.z, v.w);
     }
   } else {
+    (void)sw;
     const uint32_t a = rbase + LINE * KBLOCK_BYTES;             // line == 64-column block
     st_shared_v4(a + ((piece ^ x) << 4), v.x, v.y, v.z, v.w);
-  }
-}
-
-template <int FMT, int DQK, int LINE>
-__device__ __forceinline__ void store_lines(const uint4 (&d)[Stage<FMT, DQK>::LINES], uint32_t sK,
-                                            int row, const Geo& geo,
-                                            const uint32_t (&mul_row)[Cfg<FMT, DQK>::MUL_PER_ROW + 2]) {
-  if constexpr (LINE < Stage<FMT, DQK>::LINES) {
-    store_line<FMT, DQK, LINE>(d[LINE], sK, row, geo, mul_row);
-    store_lines<FMT, DQK, LINE + 1>(d, sK, row, geo, mul_row);
-  }
-}
-
-// The same for one line whose number is known only at run time (warp-uniform).
-template <int FMT, int DQK, int LINE = 0>
-__device__ __forceinline__ void store_one_line(const uint4& d, int line, uint32_t sK, int row,
-                                               const Geo& geo,
-                                               const uint32_t (&mul_row)[Cfg<FMT, DQK>::MUL_PER_ROW + 2]) {
-  if constexpr (LINE < Stage<FMT, DQK>::LINES) {
-    if (line == LINE) store_line<FMT, DQK, LINE>(d, sK, row, geo, mul_row);
-    else store_one_line<FMT, DQK, LINE + 1>(d, line, sK, row, geo, mul_row);
   }
 }
 
@@ -419,7 +459,7 @@ __device__ __forceinline__ void store_one_line(const uint4& d, int line, uint32_
 // Merging the splits of one request inside a thread-block cluster.
 // The `cs` CTAs of a cluster (consecutive splits, cluster dimension z) finish with
 // un-normalised O^T in TMEM, denominators l[h] and reference maxima m[h].  Each CTA
-//   1. copies its O^T, as it is, into its own shared memory as [head][d] fp32 (128 KB in
+//   1. copies its O^T, as it is, into its own shared memory as [head][d] fp32 (NH x 2 KB in
 //      the K tile region, which its own last product has released) and publishes (l, m);
 //   2. meets the others at a cluster barrier;
 //   3. reads every CTA's (l, m) through distributed shared memory and derives, per head,
@@ -431,7 +471,7 @@ __device__ __forceinline__ void store_one_line(const uint4& d, int line, uint32_
 //   5. meets the others again, so that no CTA retires while its memory is still read.
 // Partial traffic to L2 and the combine kernel's input shrink by the cluster size, and
 // with n_splits == cs there is no combine launch at all.  An empty split (no tile) takes
-// part with l = 0, m = -inf (weight 0; its memory is not read); a CTA whose bounded wait
+// part with l = 0, m = "none" (weight 0; its memory is not read); a CTA whose bounded wait
 // gave up still walks every barrier (its peers must not be left waiting) and only drops
 // its own stores.
 // ---------------------------------------------------------------------------
@@ -464,12 +504,11 @@ struct MergeOut {
   float* o_accum;
   __nv_bfloat16* out;
   int64_t stride_o_b, stride_o_s, stride_o_h, stride_lse_b, stride_lse_s, stride_lse_h;
-  long long* prof;         // debug timeline (see stamp), or null
 };
 __device__ __forceinline__ MergeOut merge_out_of(const AttnParams& p) {
   return MergeOut{p.cluster, p.n_splits, p.mode, p.sink, p.lse, p.lse_accum, p.o_accum, p.out,
                   p.stride_o_b, p.stride_o_s, p.stride_o_h, p.stride_lse_b, p.stride_lse_s,
-                  p.stride_lse_h, p.prof};
+                  p.stride_lse_h};
 }
 struct MergeCtx {
   uint32_t stage;          // shared address of the staging area (the K tile region)
@@ -478,16 +517,6 @@ struct MergeCtx {
   int64_t acc_slot0;       // (cluster index * n_req + req) * h_q + head0
   bool empty;              // this split had no tile: no TMEM, contributes zeros
 };
-
-__device__ __forceinline__ void stamp_merge(const MergeOut& p, int slot) {
-#ifdef DSV4_TIMELINE
-  if (p.prof != nullptr && (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && threadIdx.x == 0)
-    p.prof[slot] = clock64();
-#else
-  (void)p;
-  (void)slot;
-#endif
-}
 
 // Step (4) of the merge for a cluster of CS CTAs: thread = 4 consecutive d of one head; the
 // loads of BATCH items from all CS sources go out before the first is used (a remote load
@@ -499,11 +528,11 @@ __device__ __forceinline__ void pull_slices(const MergeOut& p, const Ctrl& ctrl,
   const int tid = threadIdx.x;
   const int n_items = c.heads_here * QUADS;
   __nv_bfloat16* out_base = p.out + c.bi * p.stride_o_b + c.si * p.stride_o_s + c.head0 * p.stride_o_h;
-  for (int item0 = tid; item0 < n_items; item0 += BATCH * THREADS) {
+  for (int item0 = tid < WORKERS ? tid : n_items; item0 < n_items; item0 += BATCH * WORKERS) {
     float4 v[BATCH][CS];
 #pragma unroll
     for (int k = 0; k < BATCH; ++k) {
-      const int item = item0 + k * THREADS;
+      const int item = item0 + k * WORKERS;
       const int h = item / QUADS, q = item - h * QUADS;
       const uint32_t a_loc = c.stage + (h * D_V + rank * DL + 4 * q) * 4;
 #pragma unroll
@@ -524,7 +553,7 @@ __device__ __forceinline__ void pull_slices(const MergeOut& p, const Ctrl& ctrl,
     }
 #pragma unroll
     for (int k = 0; k < BATCH; ++k) {
-      const int item = item0 + k * THREADS;
+      const int item = item0 + k * WORKERS;
       if (item >= n_items || ctrl.fail) continue;
       const int h = item / QUADS, q = item - h * QUADS;
       const int d0 = rank * DL + 4 * q;
@@ -548,6 +577,8 @@ __device__ __forceinline__ void pull_slices(const MergeOut& p, const Ctrl& ctrl,
   }
 }
 
+// `m_own` is in log2-scaled units, NEG_HUGE or -inf when the split saw nothing.
+template <int NH>
 __device__ __noinline__ void cluster_merge(const MergeOut p, Ctrl& ctrl, const MergeCtx c,
                                            float l_own, float m_own) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -556,31 +587,29 @@ __device__ __noinline__ void cluster_merge(const MergeOut p, Ctrl& ctrl, const M
   const bool final_out = p.n_splits == cs;
 
   // (1) own O^T -> own shared memory [head][d]; thread = one d (TMEM lane), 16 heads per load
-  if (tid < HEADS) {
+  if (tid < MAX_HEADS) {
     ctrl.wred[0][tid] = l_own;
-    ctrl.wred[1][tid] = m_own;
+    ctrl.wred[1][tid] = (m_own <= NEG_HUGE) ? -INFINITY : m_own;
   }
   if (!c.empty) {
     const int m = warp >> 2, lg = warp & 3;
     const int d = m * 128 + lg * 32 + lane;
 #pragma unroll 1
-    for (int c4 = 0; c4 < HEADS / 16; ++c4) {
+    for (int c4 = 0; c4 < NH / 16; ++c4) {
       uint32_t o[16];
-      tmem_ld16(c.tmem_o + m * HEADS + c4 * 16, o);
+      tmem_ld16(c.tmem_o + m * O_SLICE_COLS + c4 * 16, o);
       tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 16; ++i)
         asm volatile("st.shared.b32 [%0], %1;" ::"r"(c.stage + ((c4 * 16 + i) * D_V + d) * 4), "r"(o[i]) : "memory");
     }
   }
-  stamp_merge(p, 240);
   cluster_sync_all();                                    // (2)
-  stamp_merge(p, 241);
 
   // (3) weights of all sources for head tid.  The table (4 sources x 64 heads) reuses arrays
   // that are idle by now; wred[0] and wred[1] stay untouched, the peers are reading them.
-  float* wtab[4] = {ctrl.alpha, ctrl.wred[2], ctrl.wred[3], ctrl.mtrue};
-  if (tid < HEADS) {
+  float* wtab[4] = {ctrl.alpha, ctrl.wred[2], ctrl.wred[3], ctrl.aux};
+  if (tid < MAX_HEADS) {
     const uint32_t a_l = smem_u32(&ctrl.wred[0][tid]), a_m = smem_u32(&ctrl.wred[1][tid]);
     float ms[4], ls[4];
 #pragma unroll
@@ -617,24 +646,28 @@ __device__ __noinline__ void cluster_merge(const MergeOut p, Ctrl& ctrl, const M
     for (int r = 0; r < 4; ++r) wtab[r][tid] = w[r] * f;
   }
   __syncthreads();
-  stamp_merge(p, 242);
 
   // (4) pull this rank's slice of every source
   if (cs == 2) pull_slices<2, 8>(p, ctrl, c, wtab, rank, final_out);
   else pull_slices<4, 4>(p, ctrl, c, wtab, rank, final_out);
-  stamp_merge(p, 243);
   cluster_sync_all();                                    // (5) peers are done reading this CTA
-  stamp_merge(p, 244);
+  // A CTA whose wait gave up makes the request's result visibly invalid.
+  if (ctrl.fail && tid < c.heads_here) {
+    if (final_out) p.lse[c.bi * p.stride_lse_b + c.si * p.stride_lse_s + (c.head0 + tid) * p.stride_lse_h] = NAN;
+    else p.lse_accum[c.acc_slot0 + tid] = NAN;
+  }
 }
 
 // ---------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------
-template <int FMT, int DQK, bool EXTRA>
+template <int FMT, int DQK, int NH, bool EXTRA>
 __global__ void __launch_bounds__(THREADS, 1)
 sm100_attn_kernel(const AttnParams p) {
-  using C = Cfg<FMT, DQK>;
+  using C = Cfg<FMT, DQK, NH>;
   using S = Stage<FMT, DQK>;
+  constexpr int CPW = C::CPW;
+  constexpr int NG = C::NG;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -642,19 +675,20 @@ sm100_attn_kernel(const AttnParams p) {
   const uint32_t sK = base, sQ = base + C::K_BYTES;
   const uint32_t sP = C::P_ALIAS ? sK + (C::NB - 1) * KBLOCK_BYTES : sQ + C::Q_BYTES;
   Ctrl& ctrl = *reinterpret_cast<Ctrl*>(sm + C::K_BYTES + C::Q_BYTES + C::P_BYTES);
-  uint32_t* mul_tab = reinterpret_cast<uint32_t*>(sm + C::K_BYTES + C::Q_BYTES + C::P_BYTES + sizeof(Ctrl));
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool worker = warp < WORKER_WARPS;
   grid_dependency_wait();          // inputs may come from the kernel before this one in the stream
   if (tid == 0) stamp(p, 0);
   if (tid == 0) stamp_cta(p, 0);
   const int req = blockIdx.x, hb = blockIdx.y, split = blockIdx.z;
-  const int head0 = hb * HEADS;
-  const int heads_here = min(HEADS, p.h_q - head0);
+  const int head0 = hb * NH;
+  const int heads_here = min(NH, p.h_q - head0);
   const int bi = req / p.s_q, si = req % p.s_q;
   const bool decode = p.mode == MODE_DECODE;
   const bool mask_invalid = !decode || (p.flags & DSV4_FLAG_MASK_INVALID);
   const bool split_out = p.n_splits > 1;
+  const bool want_ml = p.max_logits != nullptr;
 
   ListView lv;
   int xlen;
@@ -674,7 +708,7 @@ sm100_attn_kernel(const AttnParams p) {
     if (tid == 0) ctrl.fail = 0;
     __syncthreads();
     MergeCtx mc{sK, 0u, heads_here, head0, bi, si, acc_slot0, true};
-    cluster_merge(merge_out_of(p), ctrl, mc, 0.f, -INFINITY);
+    cluster_merge<NH>(merge_out_of(p), ctrl, mc, 0.f, -INFINITY);
     return;
   }
   if (n_tiles == 0) {
@@ -704,119 +738,147 @@ sm100_attn_kernel(const AttnParams p) {
     return;
   }
 
-  // Set-up.  Order matters for latency: the list entries are requested first, then Q (which
-  // depends on nothing), then, as the entries arrive, the first tile's rows and their scale
-  // bytes; Q and the multipliers are written to shared memory while the rows are in flight.
+  const uint32_t bar_blk_full0 = smem_u32(&ctrl.blk_full[0]), bar_slice_free0 = smem_u32(&ctrl.slice_free[0]);
+  const uint32_t bar_s_full = smem_u32(&ctrl.s_full), bar_p_full = smem_u32(&ctrl.p_full);
+  const uint32_t bar_o_done = smem_u32(&ctrl.o_done);
+  bool ok = true;      // false once one of this thread's bounded waits has given up
+#define TSTAMP(t, k) do { if ((t) < PROF_MAX_TILES) stamp(p, PROF_TILE0 + (t) * PROF_PER_TILE + (k)); } while (0)
+
+  if (!worker) {
+    // ======================= the fifth warpgroup: MMA issue ===============================
+    // It keeps 32 registers per thread and runs no code in common with the workers from here
+    // on: only the CTA-wide (and cluster-wide) barriers, which it meets in the same order.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(ISSUER_REGS));
+    __syncthreads();                 // set-up done: barriers initialised, TMEM allocated, Q stored
+    tc_fence_after_sync();
+    if (warp == ISSUE_WARP) {
+      // Run by the whole warp, converged; one elected lane issues the MMAs and the commits
+      // (see umma_bf16_elect).
+      const uint32_t tmem_u = ctrl.tmem;
+      const uint32_t idesc_qk = make_idesc_bf16(TILE, NH, 0, 0);
+      const uint32_t idesc_pv = make_idesc_bf16(128, NH, 1, 1);
+      const uint64_t dK = make_smem_desc(sK, 16, 1024, SWZ_128B);            // K-major view
+      const uint64_t dQ = make_smem_desc(sQ, 16, 1024, SWZ_128B);
+      const uint64_t dV = make_smem_desc(sK, KBLOCK_BYTES, 1024, SWZ_128B);  // MN-major view
+      const uint64_t dP = make_smem_desc(sP, 8 * C::P_ROW_BYTES, 8 * C::P_ROW_BYTES, C::P_SWIZZLE);
+      const uint32_t elected = elect_one();
+#pragma unroll 1
+      for (int t = 0; t < n_tiles; ++t) {
+        // Q.K^T of tile t, group by group as the blocks arrive
+        static_for<0, NG>([&](auto gc) {
+          constexpr int g = decltype(gc)::value;
+          if (ok && !mbar_wait_warp(bar_blk_full0 + 8 * g, t & 1, lane)) {
+            atomicExch(&g_attn_error, ERR_BLKFULL);
+            ok = false;
+          }
+          tc_fence_after_sync();
+          if (lane == 0 && g == 0) TSTAMP(t, 1);
+#pragma unroll
+          for (int kb = 2 * g; kb < 2 * g + 2 && kb < C::NB; ++kb) {
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4)
+              umma_bf16_elect(tmem_u + COL_S, dK + static_cast<uint64_t>((kb * KBLOCK_BYTES + k4 * 32) >> 4),
+                              dQ + static_cast<uint64_t>((kb * C::QBLOCK_BYTES + k4 * 32) >> 4), idesc_qk,
+                              (kb | k4) != 0, elected);
+          }
+        });
+        umma_commit_elect(bar_s_full, elected);
+        if (lane == 0) TSTAMP(t, 2);
+        // P.V of tile t, one 128-row slice of O^T after the other
+        if (ok && !mbar_wait_warp(bar_p_full, t & 1, lane)) {
+          atomicExch(&g_attn_error, ERR_PFULL);
+          ok = false;
+        }
+        tc_fence_after_sync();
+        if (lane == 0) TSTAMP(t, 5);
+#pragma unroll 1
+        for (int mb = 0; mb < 4; ++mb) {
+#pragma unroll
+          for (int j = 0; j < KSTEPS; ++j)
+            umma_bf16_elect(tmem_u + COL_O + mb * O_SLICE_COLS,
+                            dV + static_cast<uint64_t>((j * 2048 + mb * 2 * KBLOCK_BYTES) >> 4),
+                            dP + static_cast<uint64_t>((j * 16 * C::P_ROW_BYTES) >> 4), idesc_pv,
+                            (t | j) != 0, elected);
+          umma_commit_elect(bar_slice_free0 + 8 * mb, elected);
+        }
+        if (t + 1 == n_tiles) umma_commit_elect(bar_o_done, elected);
+        if (lane == 0) TSTAMP(t, 6);
+      }
+      if (!ok) ctrl.fail = 1;
+    }
+    grid_launch_dependents();
+    // the same CTA-wide and cluster-wide barriers as the workers' epilogue, in the same order
+    __syncthreads();
+    if (p.cluster > 1) {
+      cluster_sync_all();
+      __syncthreads();
+      cluster_sync_all();
+    } else {
+      __syncthreads();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    return;
+  }
+
+  // ======================= the worker warps ===============================================
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(WORKER_REGS));
+
+  // ---- set-up ---------------------------------------------------------------------------
+  // Order matters for latency: the list entries are requested first, then Q (which depends
+  // on nothing), then, as the entries arrive, the first tile's rows and their scale bytes;
+  // Q is written to shared memory while the rows are in flight.
   S stage;
   const Geo geo{warp >> 2, 4 * (warp & 3) + (lane & 1) + 2 * (lane >> 4),
                 ((lane >> 1) & 3) + 4 * ((lane >> 3) & 1), 2 * ((lane >> 1) & 3) + ((lane >> 3) & 1)};
-  int tidx[2];       // list entries of this lane's staged rows (k-steps jsub and 4 + jsub)
-  tidx[0] = list_index<EXTRA>(lv, lv.begin + geo.row(0));
-  tidx[1] = list_index<EXTRA>(lv, lv.begin + geo.row(1));
-  // Softmax geometry: TMEM lanes 32*lg.. (tile rows), head columns 16*cg..16*cg+15.
+  // Softmax geometry: TMEM lanes 32*lg.. (tile rows), head columns CPW*cg .. +CPW.
   const int lg = warp & 3, cg = warp >> 2;
   const int row = lg * 32 + lane;
-  // The list entry of this thread's own tile row (masking; scale-table fill by tid < 128).
-  int ridx = list_index<EXTRA>(lv, lv.begin + row);
-  // List entries are fetched ahead so that no address ever waits on them: tidx / ridx
-  // belong to the tile staged in registers, tidx_next / ridx_n1 to the one after,
-  // ridx_n2 to the one after that.
-  int tidx_next[2] = {-1, -1}, ridx_n1 = -1, ridx_n2 = -1;
-  // The warp that issues the MMAs is blocked for the length of every product, so after the
-  // first tile it stages nothing: the lines of its two row groups (k-steps 3 and 7) are
-  // spread over warps 0 .. 2 LINES - 1, one line each, held in one more register set `xd`
-  // (loaded a tile ahead like the others; xidx_next is the list entry it is loaded from).
-  constexpr bool SPARE_ISSUER = S::HALVES == 2;
-  const bool has_x = SPARE_ISSUER && warp < 2 * S::LINES;
-  const int xline = warp % S::LINES;
-  const int xk = warp < S::LINES ? ISSUE_WARP >> 2 : 4 + (ISSUE_WARP >> 2);
-  const int xrow = 16 * xk + 4 * (ISSUE_WARP & 3) + (lane & 1) + 2 * (lane >> 4);
-  int xidx_next = -1;
-  uint4 xd = make_uint4(0, 0, 0, 0);
-  if (n_tiles > 1) {
-    tidx_next[0] = list_index<EXTRA>(lv, lv.begin + TILE + geo.row(0));
-    tidx_next[1] = list_index<EXTRA>(lv, lv.begin + TILE + geo.row(1));
-    ridx_n1 = ridx_n2 = list_index<EXTRA>(lv, lv.begin + TILE + row);
-    if (has_x) xidx_next = list_index<EXTRA>(lv, lv.begin + TILE + xrow);
-  }
-  // Multipliers of tile row `tid` into the table of tile `slot` (threads 0..127): one load
-  // of the row's scale bytes (issued early, `ScaleWords`), later a pair of packed factors
-  // per byte into the table.
-  struct ScaleWords { uint32_t w[C::PAGED ? KvTraits<C::PAGED ? FMT : DSV4_KV_V32>::SLOTS / 4 : 1]; };
-  auto load_scales = [&](int j, int idx) {
-    ScaleWords sw;
-    if constexpr (C::PAGED) {
-      using T = KvTraits<FMT>;
-#pragma unroll
-      for (int k = 0; k < T::SLOTS / 4; ++k) sw.w[k] = 0x7f7f7f7fu;
-      if (tid < TILE) {
-        const uint8_t* scl;
-        const uint8_t* r = row_ptr<FMT>(cache_of<EXTRA>(p, lv, j), j < lv.end ? idx : -1, scl);
-        if (r != nullptr) {
-#pragma unroll
-          for (int k = 0; k < T::SLOTS / 4; ++k) sw.w[k] = ldg_u32(reinterpret_cast<const uint32_t*>(scl) + k);
-        }
-      }
-    } else {
-      sw.w[0] = 0;
-    }
-    return sw;
-  };
-  // Ask the memory system to bring the row of list entry (j, idx) into L2 (threads 0..127, one
-  // row each; a bulk prefetch ties up no register).  Used for the second tile only, whose
-  // register loads cannot be issued before the first tile is converted: in the steady state
-  // the same prefetch a tile ahead made things slower (b = 64: 60 -> 67 us).
-  auto prefetch_row = [&](int j, int idx) {
-    if (tid < TILE && j < lv.end) {
-      const uint8_t* scl;
-      const uint8_t* r = row_ptr<FMT>(cache_of<EXTRA>(p, lv, j), idx, scl);
-      constexpr uint32_t ROW = C::PAGED ? KvTraits<C::PAGED ? FMT : DSV4_KV_V32>::ROW_BYTES : DQK * 2;
-      if (r != nullptr)
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(r), "r"(ROW) : "memory");
-    }
-  };
-  auto store_scales = [&](int slot, const ScaleWords& sw) {
-    if constexpr (C::PAGED) {
-      using T = KvTraits<FMT>;
-      if (tid < TILE) {
-        uint32_t* dst = mul_tab + (slot * TILE + tid) * C::MUL_PER_ROW;
-#pragma unroll
-        for (int k = 0; k < T::N_SCALE; ++k) {
-          const ScaleMul m = make_scale_mul((sw.w[k >> 2] >> (8 * (k & 3))) & 0xffu);
-          dst[2 * k] = m.c1;
-          dst[2 * k + 1] = m.c2 ? m.c2 : 0x3F803F80u;           // packed BF16 1.0
-        }
-      }
-    }
-  };
 
-  // ---- set-up: Q requests, barriers, TMEM, first tile -----------------------------------
+  // Tile `ld_tile` is the next one whose rows are requested from memory: its list entries are
+  // in e_ld (fetched an iteration earlier).  FP8 rows are requested a whole tile before they
+  // are stored (register staging); BF16 rows when their blocks are free (cp.async).
+  constexpr int LOAD_AHEAD = S::PAGED ? 2 : 1;
+  int e_ld[2] = {-1, -1};
+  int e_first[2] = {-1, -1};           // paged: entries of tile 0
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    if constexpr (S::PAGED) {
+      e_first[hh] = list_index<EXTRA>(lv, lv.begin + geo.row(hh));
+      if (n_tiles > 1) e_ld[hh] = list_index<EXTRA>(lv, lv.begin + TILE + geo.row(hh));
+    } else {
+      e_ld[hh] = list_index<EXTRA>(lv, lv.begin + geo.row(hh));
+    }
+  }
+  // this thread's own tile row: its list entry decides masking when invalid entries are masked
+  int ridx = 0, ridx_next = 0;
+  if (mask_invalid) ridx = list_index<EXTRA>(lv, lv.begin + row);
+
   // Q[head][d] -> blocks [d/64][head][64], 128-byte swizzle; absent heads are zero.
   const __nv_bfloat16* qrow0 = p.q + bi * p.stride_q_b + si * p.stride_q_s + head0 * p.stride_q_h;
-  constexpr int Q_CHUNKS = HEADS * C::NB * 8;
-  constexpr int Q_BATCH = (Q_CHUNKS + THREADS - 1) / THREADS;     // all in flight at once
+  constexpr int Q_CHUNKS = NH * C::NB * 8;
+  constexpr int Q_BATCH = (Q_CHUNKS + WORKERS - 1) / WORKERS;     // all in flight at once
   uint4 qv[Q_BATCH];
 #pragma unroll
   for (int it = 0; it < Q_BATCH; ++it) {
-    const int i = tid + it * THREADS;
+    const int i = tid + it * WORKERS;
     const int h = i / (C::NB * 8), cc = i % (C::NB * 8);
     qv[it] = make_uint4(0, 0, 0, 0);
     if (i < Q_CHUNKS && h < heads_here)
       qv[it] = ldg16(reinterpret_cast<const uint8_t*>(qrow0 + h * p.stride_q_h) + 16 * cc);
   }
   if (tid == 0) {
-    mbar_init(smem_u32(&ctrl.k_full), WARPS);
-    mbar_init(smem_u32(&ctrl.s_full), 1);
-    mbar_init(smem_u32(&ctrl.p_full), WARPS);
-    mbar_init(smem_u32(&ctrl.o_done), 1);
-    for (int i = 0; i < KSTEPS; ++i) mbar_init(smem_u32(&ctrl.kv_free[i]), 1);
-    ctrl.resc[0] = ctrl.resc[1] = 0;
+    for (int i = 0; i < 5; ++i) mbar_init(bar_blk_full0 + 8 * i, WORKER_WARPS);
+    for (int i = 0; i < 4; ++i) mbar_init(bar_slice_free0 + 8 * i, 1);
+    mbar_init(bar_s_full, 1);
+    mbar_init(bar_p_full, WORKER_WARPS);
+    mbar_init(bar_o_done, 1);
+    ctrl.resc = 0;
     ctrl.fail = 0;
     mbar_init_fence();
   }
-  if (tid < HEADS) {
-    ctrl.mref[tid] = -INFINITY;
-    ctrl.mtrue[tid] = -INFINITY;
+  if (tid < MAX_HEADS) {
+    ctrl.mref[tid] = NEG_HUGE;
     ctrl.alpha[tid] = 1.f;
   }
   if (warp == 0) {
@@ -824,312 +886,308 @@ sm100_attn_kernel(const AttnParams p) {
     tmem_relinquish();
   }
   // First use of the list entries: the first tile's rows and scale bytes go in flight.
+  ScaleWords<FMT> sw_cur[2], sw_ld[2];
+  const uint8_t* row_ld[2] = {nullptr, nullptr};
 #pragma unroll
-  for (int hh = 0; hh < S::HALVES; ++hh)
-    load_half<FMT, DQK, EXTRA>(stage.d[hh], p, lv, lv.begin + geo.row(hh), tidx[hh], geo);
-  const ScaleWords sw0 = load_scales(lv.begin + row, ridx);
+  for (int hh = 0; hh < 2; ++hh) {
+    sw_cur[hh].w[0] = sw_ld[hh].w[0] = NEUTRAL_SCALES;
+    if constexpr (ScaleWords<FMT>::N == 2) sw_cur[hh].w[1] = sw_ld[hh].w[1] = NEUTRAL_SCALES;
+  }
+  if constexpr (S::PAGED) {
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const uint8_t* r0 = resolve_row<FMT, EXTRA>(p, lv, lv.begin + geo.row(hh), e_first[hh], sw_cur[hh]);
+      static_for<0, S::LINES>([&](auto lc) {
+        load_line<FMT, DQK, decltype(lc)::value>(stage.d[hh][decltype(lc)::value], r0, geo);
+      });
+    }
+  }
 #pragma unroll
   for (int it = 0; it < Q_BATCH; ++it) {
-    const int i = tid + it * THREADS;
+    const int i = tid + it * WORKERS;
     const int h = i / (C::NB * 8), cc = i % (C::NB * 8), kb = cc >> 3, ch = cc & 7;
     if (i < Q_CHUNKS)
-      st_shared_v4(sQ + kb * QBLOCK_BYTES + h * 128 + ((ch ^ (h & 7)) << 4), qv[it].x, qv[it].y,
+      st_shared_v4(sQ + kb * C::QBLOCK_BYTES + h * 128 + ((ch ^ (h & 7)) << 4), qv[it].x, qv[it].y,
                    qv[it].z, qv[it].w);
   }
-  store_scales(0, sw0);
   fence_async_smem();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  // The first tile's rows have had HBM to themselves; now, while they are converted, the
-  // second tile's rows are brought into L2.
-  if (n_tiles > 1) prefetch_row(lv.begin + TILE + row, ridx_n1);
   const uint32_t tmem = ctrl.tmem;
   if (tid == 0) stamp(p, 1);
   if (tid == 0) stamp_cta(p, 1);
-#define TSTAMP(t, k) do { if ((t) < PROF_MAX_TILES) stamp(p, PROF_TILE0 + (t) * PROF_PER_TILE + (k)); } while (0)
 
-  const uint32_t bar_k_full = smem_u32(&ctrl.k_full), bar_s_full = smem_u32(&ctrl.s_full);
-  const uint32_t bar_p_full = smem_u32(&ctrl.p_full), bar_o_done = smem_u32(&ctrl.o_done);
-  const uint32_t bar_kv_free0 = smem_u32(&ctrl.kv_free[0]);
-  bool ok = true;      // false once one of this thread's bounded waits has given up
-
-  // ---- MMA issue (thread 0 only) -----------------------------------------------------
-  const uint32_t idesc_qk = make_idesc_bf16(TILE, HEADS, 0, 0);
-  const uint32_t idesc_pv = make_idesc_bf16(128, HEADS, 1, 1);
-  const uint64_t dK = make_smem_desc(sK, 16, 1024, SWZ_128B);            // K-major view
-  const uint64_t dQ = make_smem_desc(sQ, 16, 1024, SWZ_128B);
-  const uint64_t dV = make_smem_desc(sK, KBLOCK_BYTES, 1024, SWZ_128B);  // MN-major view
-  const uint64_t dP = make_smem_desc(sP, 1024, 1024, SWZ_128B);
-  // Both issue routines are run by the whole issuing warp, converged; one elected lane
-  // issues the MMAs and the commits (see umma_bf16_elect).
-  const uint32_t elected = elect_one();
-  const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
-  auto issue_qk = [&](int t, bool& ok) {
-    if (ok && !mbar_wait_warp(bar_k_full, t & 1, lane)) { atomicExch(&g_attn_error, ERR_KFULL); ok = false; }
-    tc_fence_after_sync();
-    if (lane == 0) TSTAMP(t, 1);
-#pragma unroll 1
-    for (int kb = 0; kb < C::NB; ++kb) {     // four 16-wide steps of one 64-column block
-#pragma unroll
-      for (int k4 = 0; k4 < 4; ++k4)
-        umma_bf16_elect(tmem_u + COL_S, dK + static_cast<uint64_t>((kb * KBLOCK_BYTES + k4 * 32) >> 4),
-                        dQ + static_cast<uint64_t>((kb * QBLOCK_BYTES + k4 * 32) >> 4), idesc_qk,
-                        (kb | k4) != 0, elected);
-    }
-    umma_commit_elect(bar_s_full, elected);
-  };
-  auto issue_pv = [&](int t, bool last, bool& ok) {
-    if (ok && !mbar_wait_warp(bar_p_full, t & 1, lane)) { atomicExch(&g_attn_error, ERR_PFULL); ok = false; }
-    tc_fence_after_sync();
-    if (lane == 0) TSTAMP(t, 5);
-#pragma unroll 1
-    for (int j = 0; j < KSTEPS; ++j) {       // the four 128-row slices of O^T for one k-step
-      const uint32_t acc = (t | j) != 0;
-#pragma unroll
-      for (int mb = 0; mb < 4; ++mb)
-        umma_bf16_elect(tmem_u + COL_O + mb * HEADS,
-                        dV + static_cast<uint64_t>((j * 2048 + mb * 2 * KBLOCK_BYTES) >> 4),
-                        dP + static_cast<uint64_t>((j * 2048) >> 4), idesc_pv, acc, elected);
-      umma_commit_elect(bar_kv_free0 + 8 * j, elected);
-    }
-    if (last) umma_commit_elect(bar_o_done, elected);
-  };
-
-  // ---- refill of the K tile from the staged registers -------------------------------
-  // `wait_tile` >= 0: rows of k-step j may be overwritten only once the P.V step j of
-  // that tile has retired.  After a wait has given up (`ok` false) no further wait is
-  // attempted, but every thread keeps walking the same path so that the CTA-wide
-  // barriers below stay matched; the outputs are then suppressed.
-  // As soon as a register set has been stored it is reloaded with the same rows of the
-  // next tile (list entries tidx_next; `has_next` false on the last tile), so the gather
-  // is spread over the whole P.V phase instead of hitting memory in one burst.
-  auto refill = [&](int j0, int wait_tile, int slot, bool has_next, bool& ok) {
-    const bool first = wait_tile < 0;
-    const bool spared = SPARE_ISSUER && warp == ISSUE_WARP;     // stages the first tile only
-    const bool extra = has_x && !first;
-    auto wait_free = [&](int j) {
-      if (!first && ok && !mbar_wait_warp(bar_kv_free0 + 8 * j, wait_tile & 1, lane)) {
-        atomicExch(&g_attn_error, ERR_KVFREE);
-        ok = false;
-      }
-    };
-    auto row_multipliers = [&](uint32_t (&mrow)[C::MUL_PER_ROW + 2], int trow) {
-      if constexpr (C::PAGED) {                   // one vector load each 4
-        const uint4* src = reinterpret_cast<const uint4*>(mul_tab + (slot * TILE + trow) * C::MUL_PER_ROW);
-#pragma unroll
-        for (int k = 0; k < C::MUL_PER_ROW / 4; ++k) {
-          const uint4 m4 = src[k];
-          mrow[4 * k] = m4.x; mrow[4 * k + 1] = m4.y; mrow[4 * k + 2] = m4.z; mrow[4 * k + 3] = m4.w;
-        }
-      }
-      mrow[C::MUL_PER_ROW] = mrow[C::MUL_PER_ROW + 1] = 0;
-    };
-    auto store_set = [&](const uint4 (&d)[S::LINES], int trow) {
-      uint32_t mrow[C::MUL_PER_ROW + 2];
-      row_multipliers(mrow, trow);
-      store_lines<FMT, DQK, 0>(d, sK, trow, geo, mrow);
-    };
-    auto publish = [&]() {                   // this warp's part of the tile is in shared memory
+  {
+    // ======================= the worker warps =============================================
+    // Fill of the K tile with tile `st_tile` (st_tile = t + 1 behind the P.V product of tile
+    // t, or 0 at the start), group by group.  `wait_tile` >= 0: group g may be overwritten
+    // only once P.V slice min(g, 3) of that tile has retired (block 8 carries P^T, which
+    // every slice reads).  After a wait has given up (`ok` false) no further wait is
+    // attempted, but every thread keeps walking the same path so that the barriers stay
+    // matched; the outputs are then suppressed.
+    // Paged: the rows are in registers; each line is reloaded with the same line of tile
+    // `ld_tile` as soon as it has been stored.  BF16: the rows of tile ld_tile == st_tile
+    // are copied with cp.async; group g is published once its copies have landed, which is
+    // checked after group g + 1 has been issued.
+    auto publish = [&](int g) {              // this warp's part of group g is in shared memory
       fence_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_k_full);
+      if (lane == 0) mbar_arrive(bar_blk_full0 + 8 * g);
     };
-    if (spared && !first) {
-      publish();
-      return;
-    }
-    const bool reload = has_next && !spared;
-    if constexpr (S::HALVES == 2) {
-      // Both k-steps are staged.  Each register set is reloaded as soon as it has been stored:
-      // that spreads the gather over the P.V phase (all SMs gather in step, and a burst holds
-      // the issuing warps up for as long as HBM takes to serve it).
-#pragma unroll
-      for (int jhalf = 0; jhalf < 2; ++jhalf) {
-        wait_free(4 * jhalf + geo.jsub);
-        if (lane == 0 && wait_tile == 2) stamp(p, 150 + 32 * jhalf + warp);       // k-step free
-        store_set(stage.d[jhalf], geo.row(jhalf));
-        if (reload)                        // the same rows of the next tile
-          load_half<FMT, DQK, EXTRA>(stage.d[jhalf], p, lv, j0 + TILE + geo.row(jhalf), tidx_next[jhalf], geo);
+    auto fill = [&](int wait_tile, bool load_next) {
+      bool rare = false;
+      if constexpr (S::PAGED) {
+        bool r = has_rare_scale(sw_cur[0].w[0]) || has_rare_scale(sw_cur[1].w[0]);
+        if constexpr (ScaleWords<FMT>::N == 2)
+          r = r || has_rare_scale(sw_cur[0].w[1]) || has_rare_scale(sw_cur[1].w[1]);
+        rare = __any_sync(0xffffffffu, r);
       }
-      if (extra) {                         // this warp's line of the issuing warp's rows
-        wait_free(xk);
-        uint32_t mrow[C::MUL_PER_ROW + 2];
-        row_multipliers(mrow, xrow);
-        store_one_line<FMT, DQK>(xd, xline, sK, xrow, geo, mrow);
-      }
-      publish();
-      if (lane == 0 && wait_tile == 2) stamp(p, 214 + warp);                     // arrived
-      if (has_x && has_next)
-        load_one_line<FMT, DQK, EXTRA>(xd, xline, p, lv, j0 + TILE + xrow, xidx_next, geo);
-    } else {
-      // One register set: the second k-step is loaded once the first is stored, then the
-      // first k-step of the next tile.
+      static_for<0, NG>([&](auto gc) {
+        constexpr int g = decltype(gc)::value;
+        constexpr int FREED_BY = g < 3 ? g : 3;
+        constexpr int L0 = S::first_line(g, NG), L1 = S::last_line(g, NG);
+        if (wait_tile >= 0 && ok && !mbar_wait_warp(bar_slice_free0 + 8 * FREED_BY, wait_tile & 1, lane)) {
+          atomicExch(&g_attn_error, ERR_SLICEFREE);
+          ok = false;
+        }
+        if constexpr (S::PAGED) {
+          static_for<L0, L1 + 1>([&](auto lc) {
+            constexpr int line = decltype(lc)::value;
 #pragma unroll
-      for (int jhalf = 0; jhalf < 2; ++jhalf) {
-        wait_free(4 * jhalf + geo.jsub);
-        store_set(stage.d[0], geo.row(jhalf));
-        if (jhalf == 0) {
-          load_half<FMT, DQK, EXTRA>(stage.d[0], p, lv, j0 + geo.row(1), tidx[1], geo);
+            for (int hh = 0; hh < 2; ++hh) {
+              if (rare) store_line<FMT, DQK, line, true>(stage.d[hh][line], sK, geo.row(hh), geo, sw_cur[hh]);
+              else store_line<FMT, DQK, line, false>(stage.d[hh][line], sK, geo.row(hh), geo, sw_cur[hh]);
+            }
+          });
+          publish(g);
+          if (load_next) {
+            static_for<L0, L1 + 1>([&](auto lc) {
+              constexpr int line = decltype(lc)::value;
+#pragma unroll
+              for (int hh = 0; hh < 2; ++hh) load_line<FMT, DQK, line>(stage.d[hh][line], row_ld[hh], geo);
+            });
+          }
         } else {
-          publish();
-          if (has_next)
-            load_half<FMT, DQK, EXTRA>(stage.d[0], p, lv, j0 + TILE + geo.row(0), tidx_next[0], geo);
+          static_for<L0, L1 + 1>([&](auto lc) {
+            constexpr int line = decltype(lc)::value;
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              const int r = geo.row(hh);
+              const uint32_t dst = sK + line * KBLOCK_BYTES + r * 128 + ((geo.piece_cp ^ (r & 7)) << 4);
+              const uint8_t* src = row_ld[hh] != nullptr ? row_ld[hh] + 128 * line + 16 * geo.piece_cp
+                                                         : p.kv;
+              cp_async16(dst, src, row_ld[hh] != nullptr ? 16u : 0u);
+            }
+          });
+          cp_async_commit();
+          if constexpr (g > 0) {
+            cp_async_wait<1>();
+            publish(g - 1);
+          }
+          if constexpr (g == NG - 1) {
+            cp_async_wait<0>();
+            publish(g);
+          }
         }
-      }
-    }
-  };
-
-  const uint32_t tlane = static_cast<uint32_t>(lg * 32) << 16;
-  const float cs = p.sm_scale * LOG2E;
-  float lsum[COLS_PER_WARP];
+      });
+    };
+    // Resolve the rows of the tile to load (list entries e_ld) and fetch the entries of the
+    // tile after it.
+    auto advance_loads = [&](int ld_tile) {
 #pragma unroll
-  for (int i = 0; i < COLS_PER_WARP; ++i) lsum[i] = 0.f;
+      for (int hh = 0; hh < 2; ++hh) {
+        const int j = lv.begin + ld_tile * TILE + geo.row(hh);
+        row_ld[hh] = ld_tile < n_tiles ? resolve_row<FMT, EXTRA>(p, lv, j, e_ld[hh], sw_ld[hh]) : nullptr;
+      }
+    };
+    auto fetch_entries = [&](int tile) {
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh)
+        e_ld[hh] = tile < n_tiles ? list_index<EXTRA>(lv, lv.begin + tile * TILE + geo.row(hh)) : -1;
+    };
 
+    const uint32_t tlane = static_cast<uint32_t>(lg * 32) << 16;
+    const float cs = p.sm_scale * LOG2E;
+    float lsum[CPW];
+#pragma unroll
+    for (int i = 0; i < CPW; ++i) lsum[i] = 0.f;
+    uint32_t mlpk[CPW / 2];              // running maxima of the raw scores, packed BF16 (prefill)
+#pragma unroll
+    for (int i = 0; i < CPW / 2; ++i) mlpk[i] = 0xff80ff80u;     // -inf, -inf
 
-  ScaleWords sw_next = {};
-  // Iteration t = -1 only fills the first tile; iteration t >= 0 runs tile t and, behind
-  // its P.V product, fills tile t + 1.
+    // Iteration t = -1 only fills tile 0; iteration t >= 0 runs the softmax of tile t and,
+    // behind its P.V product, fills tile t + 1.
 #pragma unroll 1
-  for (int t = -1; t < n_tiles; ++t) {
-    const bool more = t + 1 < n_tiles;
-    if (t >= 0) {
-    if (warp == ISSUE_WARP) issue_qk(t, ok);
-    if (t + 2 < n_tiles) {                       // list entries of the tile after next
-      const int j2 = lv.begin + (t + 2) * TILE;
-      tidx_next[0] = list_index<EXTRA>(lv, j2 + geo.row(0));
-      tidx_next[1] = list_index<EXTRA>(lv, j2 + geo.row(1));
-      ridx_n2 = list_index<EXTRA>(lv, j2 + row);
-      if (has_x) xidx_next = list_index<EXTRA>(lv, j2 + xrow);
-    }
-    // Is this thread's row masked (beyond the range, or an invalid entry under masking rules)?
-    bool masked = true;
-    {
-      const int j = lv.begin + t * TILE + row;
-      if (j < lv.end) {
-        const int ntok = (EXTRA && j >= lv.len) ? p.extra_n_tok : p.n_tok;
-        masked = static_cast<unsigned>(ridx) >= static_cast<unsigned>(ntok) && mask_invalid;
-      }
-    }
+    for (int t = -1; t < n_tiles; ++t) {
+      const bool more = t + 1 < n_tiles;
+      const int ld_tile = t + LOAD_AHEAD;          // tile whose rows are requested in this iteration
+      if (t >= 0) {
+        if (mask_invalid && more) ridx_next = list_index<EXTRA>(lv, lv.begin + (t + 1) * TILE + row);
+        // Is this thread's row masked (beyond the range, or an invalid entry under masking rules)?
+        bool masked = true;
+        {
+          const int j = lv.begin + t * TILE + row;
+          if (j < lv.end) {
+            const int ntok = (EXTRA && j >= lv.len) ? p.extra_n_tok : p.n_tok;
+            masked = mask_invalid && static_cast<unsigned>(ridx) >= static_cast<unsigned>(ntok);
+          }
+        }
+        const bool any_masked = __any_sync(0xffffffffu, masked);
 
-    if (ok && !mbar_wait_warp(bar_s_full, t & 1, lane)) { atomicExch(&g_attn_error, ERR_SFULL); ok = false; }
-    tc_fence_after_sync();
-    // Scale bytes of the tile after next (its list entries arrived during Q.K^T); they
-    // become multipliers at the end of this iteration.
-    if (t + 2 < n_tiles) sw_next = load_scales(lv.begin + (t + 2) * TILE + row, ridx_n2);
-    if (tid == 0) TSTAMP(t, 2);
+        if (ok && !mbar_wait_warp(bar_s_full, t & 1, lane)) { atomicExch(&g_attn_error, ERR_SFULL); ok = false; }
+        tc_fence_after_sync();
+        if (tid == 0) TSTAMP(t, 3);
 
-    // pass 1: per-head max over the tile's rows
-    {
-      uint32_t ra[16];
-      tmem_ld16(tmem + tlane + COL_S + cg * 16, ra);
-      tmem_ld_wait();
-      float v[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = masked ? -INFINITY : __uint_as_float(ra[i]);
-      const float cm = warp_col_max16_bf16(v, lane);
-      if (lane < 16) ctrl.wred[lg][cg * 16 + lane] = cm;
-    }
-    __syncthreads();
-    if (tid < HEADS) {
-      float tm = fmaxf(fmaxf(ctrl.wred[0][tid], ctrl.wred[1][tid]),
-                       fmaxf(ctrl.wred[2][tid], ctrl.wred[3][tid])) * cs;
-      ctrl.mtrue[tid] = fmaxf(ctrl.mtrue[tid], tm);
-      const float mr = ctrl.mref[tid];
-      float alpha = 1.f;
-      if (tm > mr + RESCALE_THRESHOLD) {                 // also the first finite max
-        alpha = (mr == -INFINITY) ? 0.f : ex2(mr - tm);
-        ctrl.mref[tid] = tm;
-        ctrl.resc[t & 1] = 1;
-      }
-      ctrl.alpha[tid] = alpha;
-    }
-    if (tid == 64) ctrl.resc[(t + 1) & 1] = 0;
-    __syncthreads();
-    if (tid == 0) TSTAMP(t, 3);
-
-    if (ctrl.resc[t & 1]) {
-#pragma unroll
-      for (int i = 0; i < COLS_PER_WARP; ++i) lsum[i] *= ctrl.alpha[cg * 16 + i];
-      if (t > 0) {
-        // this warp rescales slice cg of O^T for its 32 TMEM lanes
-#pragma unroll 1
-        for (int c4 = 0; c4 < HEADS / 16; ++c4) {
-          uint32_t o[16];
-          const uint32_t addr = tmem + tlane + COL_O + cg * HEADS + c4 * 16;
-          tmem_ld16(addr, o);
+        float y[CPW];
+        auto load_scores = [&](bool track_max) {
+          uint32_t s[CPW];
+          tmem_ld_cols<CPW>(tmem + tlane + COL_S + cg * CPW, s);     // warp-collective
           tmem_ld_wait();
+          if (any_masked) {                       // rare: ragged tile or masked entries
+            const uint32_t ninf = __float_as_uint(-INFINITY);
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            o[i] = __float_as_uint(__uint_as_float(o[i]) * ctrl.alpha[c4 * 16 + i]);
-          tmem_st16(addr, o);
+            for (int i = 0; i < CPW; ++i) s[i] = masked ? ninf : s[i];
+          }
+          if (track_max && want_ml) {
+#pragma unroll
+            for (int i = 0; i < CPW / 2; ++i)
+              mlpk[i] = bf16x2_max(mlpk[i], pack_bf16x2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])));
+          }
+          float ymax = -INFINITY;
+#pragma unroll
+          for (int q4 = 0; q4 < CPW / 4; ++q4) {
+            const float4 mu = *reinterpret_cast<const float4*>(&ctrl.mref[cg * CPW + q4 * 4]);
+            y[q4 * 4 + 0] = fmaf(__uint_as_float(s[q4 * 4 + 0]), cs, -mu.x);
+            y[q4 * 4 + 1] = fmaf(__uint_as_float(s[q4 * 4 + 1]), cs, -mu.y);
+            y[q4 * 4 + 2] = fmaf(__uint_as_float(s[q4 * 4 + 2]), cs, -mu.z);
+            y[q4 * 4 + 3] = fmaf(__uint_as_float(s[q4 * 4 + 3]), cs, -mu.w);
+            ymax = fmaxf(fmaxf(ymax, fmaxf(y[q4 * 4 + 0], y[q4 * 4 + 1])), fmaxf(y[q4 * 4 + 2], y[q4 * 4 + 3]));
+          }
+          return ymax;
+        };
+        const float ymax = load_scores(true);
+        // Does any score of the tile exceed its reference by more than the threshold?
+        if (bar_red_or(WORKER_BARRIER, WORKERS, ymax > RESCALE_THRESHOLD)) {
+          // Raise the references: column maxima over the tile's rows, new reference where
+          // the maximum has grown by more than the threshold (also the first finite one),
+          // O^T and the denominators scaled down to it.
+          {
+            uint32_t s[CPW];
+            tmem_ld_cols<CPW>(tmem + tlane + COL_S + cg * CPW, s);
+            tmem_ld_wait();
+            uint32_t pk[CPW / 2];
+#pragma unroll
+            for (int i = 0; i < CPW / 2; ++i) {
+              const float a = masked ? -INFINITY : __uint_as_float(s[2 * i]);
+              const float b = masked ? -INFINITY : __uint_as_float(s[2 * i + 1]);
+              pk[i] = pack_bf16x2(a, b);
+            }
+            const float cm = warp_col_max_packed<CPW>(pk, lane);
+            if (lane < CPW) ctrl.wred[lg][cg * CPW + lane] = cm;
+          }
+          if (tid == 0) ctrl.resc = 0;
+          bar_sync(WORKER_BARRIER, WORKERS);
+          if (tid < NH) {
+            const float tm = fmaxf(fmaxf(ctrl.wred[0][tid], ctrl.wred[1][tid]),
+                                   fmaxf(ctrl.wred[2][tid], ctrl.wred[3][tid])) * cs;
+            const float mr = ctrl.mref[tid];
+            float alpha = 1.f;
+            if (tm > mr + RESCALE_THRESHOLD) {
+              alpha = (mr <= NEG_HUGE) ? 0.f : ex2(mr - tm);
+              ctrl.mref[tid] = tm;
+              ctrl.resc = 1;
+            }
+            ctrl.alpha[tid] = alpha;
+          }
+          bar_sync(WORKER_BARRIER, WORKERS);
+          if (ctrl.resc) {
+#pragma unroll
+            for (int i = 0; i < CPW; ++i) lsum[i] *= ctrl.alpha[cg * CPW + i];
+            if (t > 0) {
+              // this warp rescales slice cg of O^T for its 32 TMEM lanes
+#pragma unroll 1
+              for (int c4 = 0; c4 < NH / 16; ++c4) {
+                uint32_t o[16];
+                const uint32_t addr = tmem + tlane + COL_O + cg * O_SLICE_COLS + c4 * 16;
+                tmem_ld16(addr, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                  o[i] = __float_as_uint(__uint_as_float(o[i]) * ctrl.alpha[c4 * 16 + i]);
+                tmem_st16(addr, o);
+              }
+              tmem_st_wait();
+            }
+          }
+          // (alpha / resc are rewritten only behind the next tile's barrier, which every
+          // worker reaches after it has read them here)
+          load_scores(false);
         }
-        tmem_st_wait();
+
+        // p = 2^y, denominators, this thread's part of the P^T row
+        {
+          uint32_t pk[CPW / 2];
+#pragma unroll
+          for (int i = 0; i < CPW / 2; ++i) {
+            const float p0 = ex2(y[2 * i]), p1 = ex2(y[2 * i + 1]);
+            lsum[2 * i] += p0;
+            lsum[2 * i + 1] += p1;
+            pk[i] = pack_bf16x2(p0, p1);
+          }
+          if constexpr (NH == 64) {
+            const uint32_t prow = sP + row * 128;
+            const int x = row & 7;
+            st_shared_v4(prow + (((2 * cg) ^ x) << 4), pk[0], pk[1], pk[2], pk[3]);
+            st_shared_v4(prow + (((2 * cg + 1) ^ x) << 4), pk[4], pk[5], pk[6], pk[7]);
+          } else if constexpr (NH == 32) {
+            const uint32_t prow = sP + row * 64;
+            st_shared_v4(prow + ((cg ^ ((row >> 1) & 3)) << 4), pk[0], pk[1], pk[2], pk[3]);
+          } else {
+            const uint32_t prow = sP + row * 32;
+            st_shared_v2(prow + (((cg >> 1) ^ ((row >> 2) & 1)) << 4) + (cg & 1) * 8, pk[0], pk[1]);
+          }
+        }
+        fence_async_smem();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_p_full);
+        if (tid == 0) TSTAMP(t, 4);
+        ridx = ridx_next;
+      }  // t >= 0
+
+      // fill tile t + 1 (behind the P.V product of tile t, if there is one)
+      if (more) {
+        if constexpr (S::PAGED) {
+          // registers hold tile t + 1 (scales sw_cur); they are refilled with tile t + 2
+          advance_loads(ld_tile);                       // rows of tile t + 2 from e_ld
+          fetch_entries(ld_tile + 1);
+          fill(t, ld_tile < n_tiles);
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) sw_cur[hh] = sw_ld[hh];
+        } else {
+          advance_loads(ld_tile);                       // rows of tile t + 1 from e_ld
+          fetch_entries(ld_tile + 1);
+          fill(t, true);
+        }
+        if (tid == 0) TSTAMP(t + 1, 0);
       }
     }
 
-    // pass 2: p = 2^(s*c - mref), denominators, this thread's 32 bytes of the P^T row
+    // ---- this warp's share of the final denominators (and of the logit maxima) ---------
     {
-      uint32_t s[16];
-      tmem_ld16(tmem + tlane + COL_S + cg * 16, s);   // warp-collective: all lanes take part
-      tmem_ld_wait();
-      if (__any_sync(0xffffffffu, masked)) {          // rare: ragged tile or masked entries
-        const uint32_t ninf = __float_as_uint(-INFINITY);
+      float v[CPW];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) s[i] = masked ? ninf : s[i];
-      }
-      uint32_t pk[8];
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        float4 mu = *reinterpret_cast<const float4*>(&ctrl.mref[cg * 16 + q4 * 4]);
-        mu.x = (mu.x == -INFINITY) ? 0.f : mu.x;      // nothing seen yet: any finite offset will do
-        mu.y = (mu.y == -INFINITY) ? 0.f : mu.y;
-        mu.z = (mu.z == -INFINITY) ? 0.f : mu.z;
-        mu.w = (mu.w == -INFINITY) ? 0.f : mu.w;
-        const float p0 = ex2(fmaf(__uint_as_float(s[q4 * 4 + 0]), cs, -mu.x));
-        const float p1 = ex2(fmaf(__uint_as_float(s[q4 * 4 + 1]), cs, -mu.y));
-        const float p2 = ex2(fmaf(__uint_as_float(s[q4 * 4 + 2]), cs, -mu.z));
-        const float p3 = ex2(fmaf(__uint_as_float(s[q4 * 4 + 3]), cs, -mu.w));
-        lsum[q4 * 4 + 0] += p0;
-        lsum[q4 * 4 + 1] += p1;
-        lsum[q4 * 4 + 2] += p2;
-        lsum[q4 * 4 + 3] += p3;
-        __nv_bfloat162 a = __floats2bfloat162_rn(p0, p1), b = __floats2bfloat162_rn(p2, p3);
-        pk[q4 * 2] = *reinterpret_cast<uint32_t*>(&a);
-        pk[q4 * 2 + 1] = *reinterpret_cast<uint32_t*>(&b);
-      }
-      const uint32_t prow = sP + row * 128;
-      const int x = row & 7;
-      st_shared_v4(prow + (((2 * cg) ^ x) << 4), pk[0], pk[1], pk[2], pk[3]);
-      st_shared_v4(prow + (((2 * cg + 1) ^ x) << 4), pk[4], pk[5], pk[6], pk[7]);
+      for (int i = 0; i < CPW; ++i) v[i] = lsum[i];
+      const float cm = warp_col_sum<CPW>(v, lane);
+      if (lane < CPW) ctrl.wred[lg][cg * CPW + lane] = cm;
     }
-    fence_async_smem();
-    tc_fence_before_sync();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar_p_full);
-    if (tid == 0) TSTAMP(t, 4);
-    if (warp == ISSUE_WARP) issue_pv(t, !more, ok);
-
-    }  // t >= 0
-
-    // fill tile t + 1 (behind the P.V product of tile t, if there is one)
-    if (more) {
-      refill(lv.begin + (t + 1) * TILE, t, (t + 1) & 1, t + 2 < n_tiles, ok);
-      if (tid == 0) TSTAMP(t + 1, 0);
-      if (tid == THREADS - 32) TSTAMP(t + 1, 7);
-      if (lane == 0 && t == 2) stamp(p, 230 + warp);                             // refill returned
-    }
-    // The registers now hold (or are receiving) tile t + 2: publish its multipliers (read
-    // after the two CTA barriers of the next iteration).
-    tidx[0] = tidx_next[0];
-    tidx[1] = tidx_next[1];
-    if (t >= 0 && t + 2 < n_tiles) store_scales(t & 1, sw_next);
-    if (t < 0 && n_tiles > 1) store_scales(1, load_scales(lv.begin + TILE + row, ridx_n2));
-    if (t >= 0) {
-      ridx = ridx_n1;
-      ridx_n1 = ridx_n2;
+    if (want_ml) {
+      const float mx = warp_col_max_packed<CPW>(mlpk, lane);
+      if (lane < CPW) ctrl.wmax[lg][cg * CPW + lane] = mx;
     }
   }
+#undef TSTAMP
 
   // The kernel after this one in the stream (the split combine, or the next layer) may be
   // set up on the SMs while the epilogue runs; it waits for this grid's end before it reads.
@@ -1141,67 +1199,71 @@ sm100_attn_kernel(const AttnParams p) {
   if (tid == 0) stamp(p, 3);
   if (tid == 0) stamp_cta(p, 2);
   if (!ok) ctrl.fail = 1;
-  {
-    float v[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = lsum[i];
-    const float cm = warp_col_reduce16<false>(v, lane);
-    if (lane < 16) ctrl.wred[lg][cg * 16 + lane] = cm;
-  }
   __syncthreads();
+  const uint32_t tlane_o = static_cast<uint32_t>(lg * 32) << 16;
   if (p.cluster > 1) {
     float l = 0.f, mr = -INFINITY;
-    if (tid < HEADS) {
+    if (tid < NH) {
       l = ctrl.wred[0][tid] + ctrl.wred[1][tid] + ctrl.wred[2][tid] + ctrl.wred[3][tid];
       mr = ctrl.mref[tid];
     }
-    MergeCtx mc{sK, tmem + tlane + COL_O, heads_here, head0, bi, si, acc_slot0, false};
-    cluster_merge(merge_out_of(p), ctrl, mc, l, mr);
+    MergeCtx mc{sK, tmem + tlane_o + COL_O, heads_here, head0, bi, si, acc_slot0, false};
+    cluster_merge<NH>(merge_out_of(p), ctrl, mc, l, mr);
   } else {
-  if (tid < HEADS && !ctrl.fail) {
-    const float l = ctrl.wred[0][tid] + ctrl.wred[1][tid] + ctrl.wred[2][tid] + ctrl.wred[3][tid];
-    const float mr = ctrl.mref[tid];
-    float f;
-    if (split_out) {
-      const bool empty = !(l > 0.f);
-      f = empty ? 0.f : 1.f / l;
-      if (tid < heads_here) p.lse_accum[acc_slot0 + tid] = empty ? -INFINITY : logf(l) + mr * LN2;
-    } else {
-      const bool has_sink = p.sink != nullptr;
-      float lse_v, ml_v;
-      f = finalize_row(p.mode, mr == -INFINITY ? -INFINITY : mr * LN2, l, has_sink,
-                       (has_sink && tid < heads_here) ? p.sink[head0 + tid] : 0.f, lse_v, ml_v);
-      if (tid < heads_here) {
-        p.lse[bi * p.stride_lse_b + si * p.stride_lse_s + (head0 + tid) * p.stride_lse_h] = lse_v;
-        if (p.max_logits)
-          p.max_logits[bi * p.stride_ml_b + head0 + tid] =
-              (ml_v == -INFINITY) ? -INFINITY : ctrl.mtrue[tid] * LN2;
+    if (tid < NH && !ctrl.fail) {
+      const float l = ctrl.wred[0][tid] + ctrl.wred[1][tid] + ctrl.wred[2][tid] + ctrl.wred[3][tid];
+      const float mr = ctrl.mref[tid];
+      const float m_nat = (mr <= NEG_HUGE) ? -INFINITY : mr * LN2;
+      float f;
+      if (split_out) {
+        const bool empty = !(l > 0.f) || m_nat == -INFINITY;
+        f = empty ? 0.f : 1.f / l;
+        if (tid < heads_here) p.lse_accum[acc_slot0 + tid] = empty ? -INFINITY : logf(l) + m_nat;
+      } else {
+        const bool has_sink = p.sink != nullptr;
+        float lse_v, ml_v;
+        f = finalize_row(p.mode, m_nat, l, has_sink,
+                         (has_sink && tid < heads_here) ? p.sink[head0 + tid] : 0.f, lse_v, ml_v);
+        if (tid < heads_here) {
+          p.lse[bi * p.stride_lse_b + si * p.stride_lse_s + (head0 + tid) * p.stride_lse_h] = lse_v;
+          if (want_ml) {
+            const float mx = fmaxf(fmaxf(ctrl.wmax[0][tid], ctrl.wmax[1][tid]),
+                                   fmaxf(ctrl.wmax[2][tid], ctrl.wmax[3][tid]));
+            p.max_logits[bi * p.stride_ml_b + head0 + tid] =
+                (ml_v == -INFINITY) ? -INFINITY : mx * p.sm_scale;
+          }
+        }
       }
+      ctrl.alpha[tid] = f;
     }
-    ctrl.alpha[tid] = f;
-  }
-  __syncthreads();
+    __syncthreads();
 
-  // ---- epilogue: warp w drains O^T slice w / 4 for TMEM lanes 32 * (w % 4).. --------
-  if (!ctrl.fail) {
-    const int m = warp >> 2;
-    const int d = m * 128 + lg * 32 + lane;
+    // ---- epilogue: worker warp w drains O^T slice w / 4 for TMEM lanes 32 * (w % 4).. ----
+    if (!ctrl.fail) {
+      const int m = warp >> 2;
+      const int d = m * 128 + lg * 32 + lane;
 #pragma unroll 1
-    for (int c4 = 0; c4 < HEADS / 16; ++c4) {
-      uint32_t o[16];
-      tmem_ld16(tmem + tlane + COL_O + m * HEADS + c4 * 16, o);
-      tmem_ld_wait();
+      for (int c4 = 0; c4 < NH / 16; ++c4) {
+        uint32_t o[16];
+        tmem_ld16(tmem + tlane_o + COL_O + m * O_SLICE_COLS + c4 * 16, o);
+        tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int h = c4 * 16 + i;
-        if (h < heads_here) {
-          const float val = __uint_as_float(o[i]) * ctrl.alpha[h];
-          if (split_out) p.o_accum[(acc_slot0 + h) * D_V + d] = val;
-          else out_base[h * p.stride_o_h + d] = __float2bfloat16_rn(val);
+        for (int i = 0; i < 16; ++i) {
+          const int h = c4 * 16 + i;
+          if (h < heads_here) {
+            const float val = __uint_as_float(o[i]) * ctrl.alpha[h];
+            if (split_out) p.o_accum[(acc_slot0 + h) * D_V + d] = val;
+            else out_base[h * p.stride_o_h + d] = __float2bfloat16_rn(val);
+          }
         }
       }
     }
-  }
+    // A CTA whose wait gave up wrote nothing; NaN in its log-sum-exp slots makes that
+    // visible to whatever consumes the result (the combine step propagates it).
+    if (ctrl.fail && tid < heads_here) {
+      if (split_out) p.lse_accum[acc_slot0 + tid] = NAN;
+      else p.lse[bi * p.stride_lse_b + si * p.stride_lse_s + (head0 + tid) * p.stride_lse_h] = NAN;
+    }
   }  // not clustered
 
   // ---- teardown --------------------------------------------------------------------
@@ -1211,25 +1273,33 @@ sm100_attn_kernel(const AttnParams p) {
   if (tid == 0) stamp(p, 5);
   if (tid == 0) stamp_cta(p, 3);
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+  (void)e_first;
 }
 
-template <int FMT, int DQK, bool EXTRA>
+// The dynamic shared-memory limit of a kernel is a per-device attribute: set once per
+// (instantiation, device).
+constexpr int MAX_DEVICES = 64;
+std::mutex g_configure_mu;
+
+template <int FMT, int DQK, int NH, bool EXTRA>
 cudaError_t launch_one(const AttnParams& p, cudaStream_t st) {
-  constexpr size_t smem = smem_bytes<FMT, DQK>();
-  static bool configured = false;        // per process; the attribute is per function
-  static int configured_dev = -1;
+  constexpr size_t smem = smem_bytes<FMT, DQK, NH>();
+  static bool configured[MAX_DEVICES] = {};
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (!configured || configured_dev != dev) {
-    cudaError_t e = cudaFuncSetAttribute(sm100_attn_kernel<FMT, DQK, EXTRA>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(smem));
-    if (e) return e;
-    configured = true;
-    configured_dev = dev;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e) return e;
+  if (dev < 0 || dev >= MAX_DEVICES) return cudaErrorInvalidDevice;
+  {
+    std::lock_guard<std::mutex> lk(g_configure_mu);
+    if (!configured[dev]) {
+      e = cudaFuncSetAttribute(sm100_attn_kernel<FMT, DQK, NH, EXTRA>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e) return e;
+      configured[dev] = true;
+    }
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(p.n_req, (p.h_q + HEADS - 1) / HEADS, p.n_splits);
+  cfg.gridDim = dim3(p.n_req, (p.h_q + NH - 1) / NH, p.n_splits);
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
@@ -1243,7 +1313,29 @@ cudaError_t launch_one(const AttnParams& p, cudaStream_t st) {
     attr[cfg.numAttrs].val.clusterDim.z = p.cluster;
     ++cfg.numAttrs;
   }
-  return cudaLaunchKernelEx(&cfg, sm100_attn_kernel<FMT, DQK, EXTRA>, p);
+  return cudaLaunchKernelEx(&cfg, sm100_attn_kernel<FMT, DQK, NH, EXTRA>, p);
+}
+
+// Heads per CTA (the MMA N): the smallest of 16 / 32 / 64 that holds all heads, so a
+// tensor-parallel shard of 16 heads pays for N = 16 products and a 16-head Q, not for 64.
+// DSV4_HEADS_PER_CTA=64 forces the widest shape (measurement hook).
+int heads_per_cta(int h_q) {
+  static const int forced = [] {
+    const char* e = std::getenv("DSV4_HEADS_PER_CTA");
+    return e ? std::atoi(e) : 0;
+  }();
+  if (forced == 16 || forced == 32 || forced == 64) return h_q <= forced ? forced : 64;
+  return h_q <= 16 ? 16 : h_q <= 32 ? 32 : 64;
+}
+
+template <int FMT, int DQK>
+cudaError_t launch_paged(const AttnParams& p, cudaStream_t st) {
+  if (p.extra_kv != nullptr) return launch_one<FMT, DQK, 64, true>(p, st);
+  switch (heads_per_cta(p.h_q)) {
+    case 16: return launch_one<FMT, DQK, 16, false>(p, st);
+    case 32: return launch_one<FMT, DQK, 32, false>(p, st);
+    default: return launch_one<FMT, DQK, 64, false>(p, st);
+  }
 }
 
 }  // namespace
@@ -1253,14 +1345,13 @@ bool sm100_attn_supported(int kv_format, int d_qk) {
          (kv_format == DSV4_KV_BF16 && (d_qk == 512 || d_qk == 576));
 }
 
+int sm100_attn_heads_per_cta(int h_q, bool extra) { return extra ? 64 : heads_per_cta(h_q); }
+
 cudaError_t launch_sm100_attn(const AttnParams& p, int kv_format, int d_qk, cudaStream_t st) {
-  const bool extra = p.extra_kv != nullptr;
-  if (kv_format == DSV4_KV_MODEL1)
-    return extra ? launch_one<DSV4_KV_MODEL1, 512, true>(p, st) : launch_one<DSV4_KV_MODEL1, 512, false>(p, st);
-  if (kv_format == DSV4_KV_V32)
-    return extra ? launch_one<DSV4_KV_V32, 576, true>(p, st) : launch_one<DSV4_KV_V32, 576, false>(p, st);
-  if (d_qk == 512) return launch_one<DSV4_KV_BF16, 512, false>(p, st);
-  return launch_one<DSV4_KV_BF16, 576, false>(p, st);
+  if (kv_format == DSV4_KV_MODEL1) return launch_paged<DSV4_KV_MODEL1, 512>(p, st);
+  if (kv_format == DSV4_KV_V32) return launch_paged<DSV4_KV_V32, 576>(p, st);
+  if (d_qk == 512) return launch_one<DSV4_KV_BF16, 512, 64, false>(p, st);
+  return launch_one<DSV4_KV_BF16, 576, 64, false>(p, st);
 }
 
 cudaError_t read_attn_error(int* value, bool reset) {

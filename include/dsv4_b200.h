@@ -30,7 +30,7 @@ enum Dsv4Status {
   DSV4_ERR_ALIGN = 4,       /* a pointer or stride breaks an alignment rule    */
   DSV4_ERR_ARCH = 5,        /* the current device is not sm_100                */
   DSV4_ERR_CUDA = 6,        /* a CUDA runtime call failed (see dsv4_last_cuda_error) */
-  DSV4_ERR_SCRATCH = 7,     /* n_splits > 1 but scratch pointers are null      */
+  DSV4_ERR_SCRATCH = 7,     /* partials leave the chip but scratch pointers are null */
   DSV4_ERR_UNSUPPORTED = 8, /* valid request that this build does not implement */
   DSV4_ERR_SCRATCH_TOO_LARGE = 9 /* dsv4_sparse_decode_noalloc: partials exceed the built-in scratch */
 };
@@ -108,8 +108,8 @@ typedef struct Dsv4DecodeArgs {
 
   void* out;                    /* BF16 [b, s_q, h_q, 512]                       */
   float* lse;                   /* fp32, addressed with the three lse strides    */
-  float* o_accum;               /* scratch, n_splits > 1                         */
-  float* lse_accum;             /* scratch, n_splits > 1                         */
+  float* o_accum;               /* scratch, dsv4_decode_partial_sets(args) > 1   */
+  float* lse_accum;             /* scratch, dsv4_decode_partial_sets(args) > 1   */
 
   int64_t stride_q_b, stride_q_s, stride_q_h;
   int64_t stride_kv_block, stride_extra_kv_block;

@@ -5,9 +5,13 @@ Every case runs the CUDA path through the C ABI at the full size of the
 configuration and compares with the CPU oracle on the gathered rows only
 (`whole_arena=False`: the same arithmetic without dequantising the whole cache).
 The caches are filled on the GPU by the store kernel, which is checked bit for
-bit against the oracle's quantiser in test_gpu_parts.py.  Tolerances: out
-atol = rtol = 5e-3 and max relative error <= 2e-2, lse 1e-3 (decode), 1e-2
-(prefill max_logits / lse), as in the reference's own tests.
+bit against the oracle's quantiser in test_gpu_parts.py.  Tolerances: lse 1e-3
+(decode), 1e-2 (prefill max_logits / lse) as in the reference's own tests; out
+max relative error <= 2e-2 and element-wise atol 5e-3 with rtol 2^-7.  The
+reference's tests use rtol 5e-3 on inputs scaled down so that outputs stay well
+below 1; the configurations here draw latents from N(0, 1), outputs reach 2..4,
+where one BF16 unit in the last place is 0.0156 = 2^-7 relative, and two correct
+fp32 results that straddle a rounding boundary differ by exactly that.
 """
 import math
 
@@ -20,6 +24,7 @@ from util import arena2d, max_rel_err
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
+OUT_RTOL = 2.0 ** -7          # one BF16 unit in the last place
 
 
 @pytest.fixture(scope="module")
@@ -33,7 +38,7 @@ def check_decode(K, out, lse, out_ref, lse_ref):
     assert K.device_status() == 0, "a bounded wait inside the kernel gave up"
     out, lse = out.cpu(), lse.cpu().transpose(1, 2)
     torch.testing.assert_close(lse, lse_ref, atol=1e-3, rtol=1e-3)
-    torch.testing.assert_close(out.float(), out_ref.float(), atol=5e-3, rtol=5e-3)
+    torch.testing.assert_close(out.float(), out_ref.float(), atol=5e-3, rtol=OUT_RTOL)
     assert max_rel_err(out, out_ref) <= 2e-2
 
 
@@ -149,7 +154,7 @@ def check_prefill(K, got, ref):
     out_ref, mx_ref, lse_ref = ref
     cos = torch.nn.functional.cosine_similarity(out.float().flatten(), out_ref.float().flatten(), dim=0)
     assert cos >= 0.999
-    torch.testing.assert_close(out.float(), out_ref.float(), atol=5e-3, rtol=5e-3)
+    torch.testing.assert_close(out.float(), out_ref.float(), atol=5e-3, rtol=OUT_RTOL)
     assert max_rel_err(out, out_ref) <= 2e-2
     for a, b in ((mx, mx_ref), (lse, lse_ref)):
         assert torch.equal(torch.isfinite(a), torch.isfinite(b))
@@ -222,9 +227,10 @@ SCALE_BYTES = [0, 1, 2, 100, 118, 125, 126, 127, 128, 133, 134, 135, 140, 200, 2
 
 @pytest.mark.parametrize("layout", [O.MODEL1, O.V32], ids=["model1", "v32"])
 @pytest.mark.parametrize("h_q", [16, 64])
-def test_single_entry_lists_return_the_value_row_bit_for_bit(K, layout, h_q):
+def test_single_entry_lists_return_the_value_row_exactly(K, layout, h_q):
     """With a one-entry list the softmax weight is exactly 1, so `out` must equal the BF16 V
-    row (first 512 dequantised columns) bit for bit: this checks the attention kernel's own
+    row (first 512 dequantised columns) exactly (as values: a sum of products cannot keep the
+    sign of a zero, so -0 comes back as +0): this checks the attention kernel's own
     gather, FP8 x UE8M0 -> BF16 conversion and swizzled shared-memory staging, for every
     e4m3 code under scale bytes that include 0 and values above 134 (where one packed
     multiply does not cover the range).  Scales are kept where the product stays finite and
@@ -264,7 +270,7 @@ def test_single_entry_lists_return_the_value_row_bit_for_bit(K, layout, h_q):
     got = out.cpu()[:, 0]                                                # [n, h_q, 512]
     first_scale = sb[order // 64]                                        # scale byte of tile 0 per request
     for h in (0, h_q // 2, h_q - 1):
-        bad = (got[:, h].view(torch.int16) != want.view(torch.int16)).any(dim=1)
+        bad = (got[:, h].float() != want.float()).any(dim=1)
         assert not bad.any(), (f"head {h}: {int(bad.sum())} rows differ; first-tile scale bytes "
                                f"of those rows: {sorted(set(first_scale[bad].tolist()))}")
     assert torch.equal(lse.cpu(), torch.zeros_like(lse.cpu()))
