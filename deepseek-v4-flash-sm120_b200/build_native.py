@@ -35,7 +35,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     cmd = [nvcc, "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
            "-shared", "-Xcompiler", "-fPIC", "-I" + os.path.join(ROOT, "include"), "-I" + CSRC,
-           "--threads", "4"]
+           "--threads", "4", "-diag-suppress", "177"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     if os.environ.get("DSV4_EXTRA_DEFINES"):

@@ -117,6 +117,10 @@ struct Ctrl {
   float alpha[MAX_HEADS];                // rescale factor / final output factor
   float aux[MAX_HEADS];                  // fourth weight table of the cluster merge
   float wmax[4][MAX_HEADS];              // per-lane-group column maxima of the raw scores (prefill)
+  // Where the rows of the tiles being loaded live: one entry per tile row (row start or
+  // null, scale bytes or null), written by one thread per row, read by the eight threads
+  // that stage the row.  Two tiles, alternating.
+  alignas(16) const uint8_t* rows[2][TILE][2];
 };
 
 template <int FMT, int DQK, int NH>
@@ -232,16 +236,17 @@ __device__ __forceinline__ void stamp(const AttnParams& p, int slot) {
   (void)slot;
 #endif
 }
-constexpr int PROF_TILE0 = 8, PROF_PER_TILE = 8, PROF_MAX_TILES = 24;
-// Per-CTA wall-clock stamps (global timer, ns) at slots 256 + 4 * cta + k; the buffer holds
-// 256 + 4 * CTAs values.
+constexpr int PROF_TILE0 = 8, PROF_PER_TILE = 32, PROF_MAX_TILES = 30;
+constexpr int PROF_CTA0 = 1024;
+// Per-CTA wall-clock stamps (global timer, ns) at slots 1024 + 4 * cta + k; the buffer holds
+// 1024 + 4 * CTAs values.
 __device__ __forceinline__ void stamp_cta(const AttnParams& p, int k) {
 #ifdef DSV4_TIMELINE
   if (p.prof != nullptr) {
     const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    p.prof[256 + 4 * cta + k] = static_cast<long long>(t);
+    p.prof[PROF_CTA0 + 4 * cta + k] = static_cast<long long>(t);
   }
 #else
   (void)p;
@@ -350,28 +355,17 @@ template <int FMT> struct ScaleWords {
 };
 constexpr uint32_t NEUTRAL_SCALES = 0x7f7f7f7fu;       // 2^0 in every byte
 
-// A word holds a scale byte that one packed multiply cannot apply: 0 or above 134.
-__device__ __forceinline__ bool has_rare_scale(uint32_t w) {
-  return __vcmpeq4(w, 0u) != 0u || __vcmpgtu4(w, 0x86868686u) != 0u;
-}
-
-// Row pointer and scale words of list entry (j, idx).
-template <int FMT, bool EXTRA>
-__device__ __forceinline__ const uint8_t* resolve_row(const AttnParams& p, const ListView& lv, int j,
-                                                      int idx, ScaleWords<FMT>& sw) {
-  const uint8_t* scl;
-  const uint8_t* row = row_ptr<FMT>(cache_of<EXTRA>(p, lv, j), idx, scl);
+// Scale words of a row from the address of its scale bytes (null: neutral scales).
+template <int FMT>
+__device__ __forceinline__ void load_scale_words(ScaleWords<FMT>& sw, const uint8_t* scl) {
 #pragma unroll
   for (int k = 0; k < ScaleWords<FMT>::N; ++k) sw.w[k] = NEUTRAL_SCALES;
   if constexpr (FMT != DSV4_KV_BF16) {
-    if (row != nullptr) {
+    if (scl != nullptr) {
 #pragma unroll
       for (int k = 0; k < ScaleWords<FMT>::N; ++k) sw.w[k] = ldg_u32(scl + 4 * k);
-      // the eighth slot of the 584-byte layout is padding, not a scale
-      if constexpr (FMT == DSV4_KV_MODEL1) sw.w[1] = (sw.w[1] & 0x00ffffffu) | 0x7f000000u;
     }
   }
-  return row;
 }
 
 // Issue the load of this lane's chunk of line LINE of `row` (null: zeros).
@@ -384,22 +378,32 @@ __device__ __forceinline__ void load_line(uint4& d, const uint8_t* row, const Ge
     d = ldg16(row + 16 * piece + 128 * LINE);
 }
 
-// e4m3 -> BF16 with the block scale, two values per packed multiply.  The byte, sign-
-// extended to 16 bits and shifted left by four, has the e4m3 magnitude bits where a BF16
-// word reads them as value * 2^-120 (normals and subnormals alike) and the sign in bit 15;
-// c1 = 2^(s - 7) in both halves then rescales and applies the UE8M0 scale in one exact
-// multiply (the product has at most four significant bits).
-// (prmt through inline PTX: __byte_perm drops the selector bit that asks for the sign.)
+// e4m3 -> BF16 with the block scale.  The byte, sign-extended to 16 bits and shifted left by
+// four, has the e4m3 magnitude bits where a BF16 word reads them as value * 2^-120 (normals
+// and subnormals alike) and the sign in bit 15.  Two packed multiplies then rescale and apply
+// the UE8M0 scale 2^(s-127) for EVERY scale byte, each of them exact (the value has at most
+// four significant bits) unless the result leaves the BF16 range, where the single rounding
+// is the same as that of an fp32 product rounded to BF16:
+//   s <= 127:  c1 = 2^(s-7),  c2 = 1;       s > 127:  c1 = 2^120 (giving the e4m3 value itself),
+//   c2 = 2^(s-127).
+// Branch-free and on the FMA pipe, which this kernel leaves idle; the integer pipe is the
+// busy one.  (prmt through inline PTX: __byte_perm drops the selector bit that asks for the
+// sign.)
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t d;
   asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
   return d;
 }
-__device__ __forceinline__ void dequant4(uint32_t w, uint32_t c1, uint32_t& lo, uint32_t& hi) {
+struct ScalePair { uint32_t c1, c2; };               // packed BF16 factors
+__device__ __forceinline__ ScalePair scale_pair(uint32_t s) {
+  const uint32_t e1 = min(s + 120u, 247u);
+  return ScalePair{e1 * 0x00800080u, (s + 247u - e1) * 0x00800080u};
+}
+__device__ __forceinline__ void dequant4(uint32_t w, const ScalePair& c, uint32_t& lo, uint32_t& hi) {
   const uint32_t t0 = prmt(w, 0u, 0x9180u);           // [b0, sign(b0), b1, sign(b1)]
   const uint32_t t1 = prmt(w, 0u, 0xB3A2u);           // [b2, sign(b2), b3, sign(b3)]
-  lo = bf16x2_mul((t0 << 4) & 0x87F087F0u, c1);
-  hi = bf16x2_mul((t1 << 4) & 0x87F087F0u, c1);
+  lo = bf16x2_mul(bf16x2_mul((t0 << 4) & 0x87F087F0u, c.c1), c.c2);
+  hi = bf16x2_mul(bf16x2_mul((t1 << 4) & 0x87F087F0u, c.c1), c.c2);
 }
 
 // Scale byte that applies to this lane's FP8 chunk of line LINE.
@@ -412,9 +416,8 @@ __device__ __forceinline__ uint32_t scale_byte_of(const ScaleWords<FMT>& sw, int
   }
 }
 
-// Convert and store line LINE of the staged row `v` (tile row `row`).  RARE selects the
-// two-multiply form that also covers scale bytes 0 and above 134.
-template <int FMT, int DQK, int LINE, bool RARE>
+// Convert and store line LINE of the staged row `v` (tile row `row`).
+template <int FMT, int DQK, int LINE>
 __device__ __forceinline__ void store_line(const uint4& v, uint32_t sK, int row, const Geo& geo,
                                            const ScaleWords<FMT>& sw) {
   using S = Stage<FMT, DQK>;
@@ -426,22 +429,17 @@ __device__ __forceinline__ void store_line(const uint4& v, uint32_t sK, int row,
   if constexpr (S::PAGED) {
     constexpr bool ALL_FP8 = 8 * LINE + 7 < S::FP8_CH, NO_FP8 = 8 * LINE >= S::FP8_CH;
     if (ALL_FP8 || (!NO_FP8 && ci < S::FP8_CH)) {
-      const uint32_t s = scale_byte_of<FMT, LINE>(sw, piece);
-      uint32_t o[8];
-      if constexpr (!RARE) {
-        const uint32_t c1 = (s + 120u) * 0x00800080u;             // packed BF16 2^(s-7)
-        dequant4(v.x, c1, o[0], o[1]);
-        dequant4(v.y, c1, o[2], o[3]);
-        dequant4(v.z, c1, o[4], o[5]);
-        dequant4(v.w, c1, o[6], o[7]);
-      } else {
-        const ScaleMul m = make_scale_mul(s);
-        dequant4_fast(v.x, m, o[0], o[1]);
-        dequant4_fast(v.y, m, o[2], o[3]);
-        dequant4_fast(v.z, m, o[4], o[5]);
-        dequant4_fast(v.w, m, o[6], o[7]);
-      }
+      const ScalePair c = scale_pair(scale_byte_of<FMT, LINE>(sw, piece));
       const uint32_t a = rbase + (ci >> 2) * KBLOCK_BYTES + (((2 * (ci & 3)) ^ x) << 4);
+      uint32_t o[8];
+#ifdef EXP_NOCONV
+      o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w; o[4] = v.x ^ c.c1; o[5] = v.y; o[6] = v.z; o[7] = v.w ^ c.c2;
+#else
+      dequant4(v.x, c, o[0], o[1]);
+      dequant4(v.y, c, o[2], o[3]);
+      dequant4(v.z, c, o[4], o[5]);
+      dequant4(v.w, c, o[6], o[7]);
+#endif
       st_shared_v4(a, o[0], o[1], o[2], o[3]);
       st_shared_v4(a ^ 16, o[4], o[5], o[6], o[7]);             // the neighbouring chunk
     } else if (ci < S::CH) {
@@ -659,6 +657,68 @@ __device__ __noinline__ void cluster_merge(const MergeOut p, Ctrl& ctrl, const M
 }
 
 // ---------------------------------------------------------------------------
+// Raising the softmax references (all 512 workers; the first tile, and any tile in which
+// some score exceeds its head's reference by more than the threshold).  Column maxima of
+// S^T over the tile's rows (BF16-rounded: the reference only has to be the same for every
+// thread, not exact), a new reference where the maximum has grown by more than the
+// threshold (also the first finite one), and O^T in TMEM scaled down to it; the factors
+// stay in ctrl.alpha (ctrl.resc says whether any differs from one) for the caller's
+// denominators.  Out of line on purpose: it is rare, and the tile loop must stay small.
+// `tmem_lanes` is the TMEM base address with this warp's lane offset applied.
+// ---------------------------------------------------------------------------
+template <int NH>
+__device__ __noinline__ void raise_references(Ctrl& ctrl, uint32_t tmem_lanes, bool masked, float cs,
+                                              bool rescale_o) {
+  constexpr int CPW = NH / 4;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int lg = warp & 3, cg = warp >> 2;
+  {
+    uint32_t s[CPW];
+    tmem_ld_cols<CPW>(tmem_lanes + COL_S + cg * CPW, s);
+    tmem_ld_wait();
+    uint32_t pk[CPW / 2];
+#pragma unroll
+    for (int i = 0; i < CPW / 2; ++i) {
+      const float a = masked ? -INFINITY : __uint_as_float(s[2 * i]);
+      const float b = masked ? -INFINITY : __uint_as_float(s[2 * i + 1]);
+      pk[i] = pack_bf16x2(a, b);
+    }
+    const float cm = warp_col_max_packed<CPW>(pk, lane);
+    if (lane < CPW) ctrl.wred[lg][cg * CPW + lane] = cm;
+  }
+  if (tid == 0) ctrl.resc = 0;
+  bar_sync(WORKER_BARRIER, WORKERS);
+  if (tid < NH) {
+    const float tm = fmaxf(fmaxf(ctrl.wred[0][tid], ctrl.wred[1][tid]),
+                           fmaxf(ctrl.wred[2][tid], ctrl.wred[3][tid])) * cs;
+    const float mr = ctrl.mref[tid];
+    float alpha = 1.f;
+    if (tm > mr + RESCALE_THRESHOLD) {
+      alpha = (mr <= NEG_HUGE) ? 0.f : ex2(mr - tm);
+      ctrl.mref[tid] = tm;
+      ctrl.resc = 1;
+    }
+    ctrl.alpha[tid] = alpha;
+  }
+  bar_sync(WORKER_BARRIER, WORKERS);
+  if (ctrl.resc && rescale_o) {
+    // this warp rescales slice cg of O^T for its 32 TMEM lanes
+#pragma unroll 1
+    for (int c4 = 0; c4 < NH / 16; ++c4) {
+      uint32_t o[16];
+      const uint32_t addr = tmem_lanes + COL_O + cg * O_SLICE_COLS + c4 * 16;
+      tmem_ld16(addr, o);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        o[i] = __float_as_uint(__uint_as_float(o[i]) * ctrl.alpha[c4 * 16 + i]);
+      tmem_st16(addr, o);
+    }
+    tmem_st_wait();
+  }
+}
+
+// ---------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------
 template <int FMT, int DQK, int NH, bool EXTRA>
@@ -764,7 +824,9 @@ sm100_attn_kernel(const AttnParams p) {
       const uint32_t elected = elect_one();
 #pragma unroll 1
       for (int t = 0; t < n_tiles; ++t) {
-        // Q.K^T of tile t, group by group as the blocks arrive
+        // Q.K^T of tile t, group by group as the blocks arrive.  The issue loops are fully
+        // unrolled on purpose: issuing is what bounds the tensor pipe at N <= 64 (about 50 clk
+        // per MMA unrolled, 75 rolled, against 30 clk of execution).
         static_for<0, NG>([&](auto gc) {
           constexpr int g = decltype(gc)::value;
           if (ok && !mbar_wait_warp(bar_blk_full0 + 8 * g, t & 1, lane)) {
@@ -784,6 +846,13 @@ sm100_attn_kernel(const AttnParams p) {
         });
         umma_commit_elect(bar_s_full, elected);
         if (lane == 0) TSTAMP(t, 2);
+#ifdef DSV4_TIMELINE
+        if (lane == 0) {                 // when does the commit really arrive? (pure spin)
+          for (int i = 0; i < (1 << 20) && !mbar_test(bar_s_full, t & 1); ++i) {}
+          TSTAMP(t, 18);
+        }
+        __syncwarp();
+#endif
         // P.V of tile t, one 128-row slice of O^T after the other
         if (ok && !mbar_wait_warp(bar_p_full, t & 1, lane)) {
           atomicExch(&g_attn_error, ERR_PFULL);
@@ -803,6 +872,15 @@ sm100_attn_kernel(const AttnParams p) {
         }
         if (t + 1 == n_tiles) umma_commit_elect(bar_o_done, elected);
         if (lane == 0) TSTAMP(t, 6);
+#ifdef DSV4_TIMELINE
+        if (lane == 0) {
+          for (int mb = 0; mb < 4; ++mb) {
+            for (int i = 0; i < (1 << 20) && !mbar_test(bar_slice_free0 + 8 * mb, t & 1); ++i) {}
+            TSTAMP(t, 19 + mb);
+          }
+        }
+        __syncwarp();
+#endif
       }
       if (!ok) ctrl.fail = 1;
     }
@@ -835,20 +913,24 @@ sm100_attn_kernel(const AttnParams p) {
   const int lg = warp & 3, cg = warp >> 2;
   const int row = lg * 32 + lane;
 
-  // Tile `ld_tile` is the next one whose rows are requested from memory: its list entries are
-  // in e_ld (fetched an iteration earlier).  FP8 rows are requested a whole tile before they
-  // are stored (register staging); BF16 rows when their blocks are free (cp.async).
+  // Rows are requested from memory LOAD_AHEAD tiles before they are stored: FP8 rows a whole
+  // tile ahead (register staging), BF16 rows when their blocks are free (cp.async).  Where
+  // the rows of a tile live is worked out once per row, by thread `tid` < 128 for tile row
+  // `tid`, and handed to the staging threads through ctrl.rows; the list entry it starts
+  // from is fetched an iteration earlier (e_pref).
   constexpr int LOAD_AHEAD = S::PAGED ? 2 : 1;
-  int e_ld[2] = {-1, -1};
-  int e_first[2] = {-1, -1};           // paged: entries of tile 0
-#pragma unroll
-  for (int hh = 0; hh < 2; ++hh) {
-    if constexpr (S::PAGED) {
-      e_first[hh] = list_index<EXTRA>(lv, lv.begin + geo.row(hh));
-      if (n_tiles > 1) e_ld[hh] = list_index<EXTRA>(lv, lv.begin + TILE + geo.row(hh));
-    } else {
-      e_ld[hh] = list_index<EXTRA>(lv, lv.begin + geo.row(hh));
-    }
+  auto write_rows = [&](int tile, int entry) {           // threads 0..127
+    const uint8_t* scl;
+    const int j = lv.begin + tile * TILE + tid;
+    const uint8_t* r = row_ptr<FMT>(cache_of<EXTRA>(p, lv, j), entry, scl);
+    *reinterpret_cast<ulonglong2*>(&ctrl.rows[tile & 1][tid][0]) =
+        make_ulonglong2(reinterpret_cast<unsigned long long>(r), reinterpret_cast<unsigned long long>(scl));
+  };
+  int e_pref = -1;
+  if (tid < TILE) {
+    const int first = LOAD_AHEAD - 1;                    // the tile the first fill requests
+    if (first < n_tiles) write_rows(first, list_index<EXTRA>(lv, lv.begin + first * TILE + tid));
+    if (first + 1 < n_tiles) e_pref = list_index<EXTRA>(lv, lv.begin + (first + 1) * TILE + tid);
   }
   // this thread's own tile row: its list entry decides masking when invalid entries are masked
   int ridx = 0, ridx_next = 0;
@@ -894,9 +976,13 @@ sm100_attn_kernel(const AttnParams p) {
     if constexpr (ScaleWords<FMT>::N == 2) sw_cur[hh].w[1] = sw_ld[hh].w[1] = NEUTRAL_SCALES;
   }
   if constexpr (S::PAGED) {
+    // tile 0 is requested at once, by the staging threads themselves
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
-      const uint8_t* r0 = resolve_row<FMT, EXTRA>(p, lv, lv.begin + geo.row(hh), e_first[hh], sw_cur[hh]);
+      const int j = lv.begin + geo.row(hh);
+      const uint8_t* scl;
+      const uint8_t* r0 = row_ptr<FMT>(cache_of<EXTRA>(p, lv, j), list_index<EXTRA>(lv, j), scl);
+      load_scale_words<FMT>(sw_cur[hh], scl);
       static_for<0, S::LINES>([&](auto lc) {
         load_line<FMT, DQK, decltype(lc)::value>(stage.d[hh][decltype(lc)::value], r0, geo);
       });
@@ -936,31 +1022,33 @@ sm100_attn_kernel(const AttnParams p) {
       if (lane == 0) mbar_arrive(bar_blk_full0 + 8 * g);
     };
     auto fill = [&](int wait_tile, bool load_next) {
-      bool rare = false;
-      if constexpr (S::PAGED) {
-        bool r = has_rare_scale(sw_cur[0].w[0]) || has_rare_scale(sw_cur[1].w[0]);
-        if constexpr (ScaleWords<FMT>::N == 2)
-          r = r || has_rare_scale(sw_cur[0].w[1]) || has_rare_scale(sw_cur[1].w[1]);
-        rare = __any_sync(0xffffffffu, r);
-      }
       static_for<0, NG>([&](auto gc) {
         constexpr int g = decltype(gc)::value;
         constexpr int FREED_BY = g < 3 ? g : 3;
         constexpr int L0 = S::first_line(g, NG), L1 = S::last_line(g, NG);
-        if (wait_tile >= 0 && ok && !mbar_wait_warp(bar_slice_free0 + 8 * FREED_BY, wait_tile & 1, lane)) {
+        if (wait_tile >= 0 && ok && !mbar_wait(bar_slice_free0 + 8 * FREED_BY, wait_tile & 1)) {
           atomicExch(&g_attn_error, ERR_SLICEFREE);
           ok = false;
         }
+        if (tid == 0) TSTAMP(wait_tile + 1, 8 + 2 * g);
         if constexpr (S::PAGED) {
           static_for<L0, L1 + 1>([&](auto lc) {
             constexpr int line = decltype(lc)::value;
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
-              if (rare) store_line<FMT, DQK, line, true>(stage.d[hh][line], sK, geo.row(hh), geo, sw_cur[hh]);
-              else store_line<FMT, DQK, line, false>(stage.d[hh][line], sK, geo.row(hh), geo, sw_cur[hh]);
+              store_line<FMT, DQK, line>(stage.d[hh][line], sK, geo.row(hh), geo, sw_cur[hh]);
             }
           });
+          if (tid == 0 && g == 1) TSTAMP(wait_tile + 1, 24);
+#ifdef DSV4_TIMELINE
+          if (g == 1) {
+            fence_async_smem();
+            if (tid == 0) TSTAMP(wait_tile + 1, 25);
+          }
+#endif
           publish(g);
+          if (tid == 0) TSTAMP(wait_tile + 1, 9 + 2 * g);
+#if !defined(EXP_BURST) && !defined(EXP_NOLOAD)
           if (load_next) {
             static_for<L0, L1 + 1>([&](auto lc) {
               constexpr int line = decltype(lc)::value;
@@ -968,6 +1056,8 @@ sm100_attn_kernel(const AttnParams p) {
               for (int hh = 0; hh < 2; ++hh) load_line<FMT, DQK, line>(stage.d[hh][line], row_ld[hh], geo);
             });
           }
+#endif
+          if (tid == 0 && g == 1) TSTAMP(wait_tile + 1, 27);
         } else {
           static_for<L0, L1 + 1>([&](auto lc) {
             constexpr int line = decltype(lc)::value;
@@ -992,19 +1082,20 @@ sm100_attn_kernel(const AttnParams p) {
         }
       });
     };
-    // Resolve the rows of the tile to load (list entries e_ld) and fetch the entries of the
-    // tile after it.
+    // Where the rows of tile `ld_tile` live (ctrl.rows, written before the barrier this
+    // thread last passed), and their scale bytes on the way.
     auto advance_loads = [&](int ld_tile) {
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
-        const int j = lv.begin + ld_tile * TILE + geo.row(hh);
-        row_ld[hh] = ld_tile < n_tiles ? resolve_row<FMT, EXTRA>(p, lv, j, e_ld[hh], sw_ld[hh]) : nullptr;
+        row_ld[hh] = nullptr;
+        const uint8_t* scl = nullptr;
+        if (ld_tile < n_tiles) {
+          const ulonglong2 e = *reinterpret_cast<const ulonglong2*>(&ctrl.rows[ld_tile & 1][geo.row(hh)][0]);
+          row_ld[hh] = reinterpret_cast<const uint8_t*>(e.x);
+          scl = reinterpret_cast<const uint8_t*>(e.y);
+        }
+        load_scale_words<FMT>(sw_ld[hh], scl);
       }
-    };
-    auto fetch_entries = [&](int tile) {
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh)
-        e_ld[hh] = tile < n_tiles ? list_index<EXTRA>(lv, lv.begin + tile * TILE + geo.row(hh)) : -1;
     };
 
     const uint32_t tlane = static_cast<uint32_t>(lg * 32) << 16;
@@ -1023,6 +1114,11 @@ sm100_attn_kernel(const AttnParams p) {
       const bool more = t + 1 < n_tiles;
       const int ld_tile = t + LOAD_AHEAD;          // tile whose rows are requested in this iteration
       if (t >= 0) {
+        // rows of the tile this iteration's fill requests (published by the barrier below)
+        if (tid < TILE) {
+          if (ld_tile < n_tiles) write_rows(ld_tile, e_pref);
+          if (ld_tile + 1 < n_tiles) e_pref = list_index<EXTRA>(lv, lv.begin + (ld_tile + 1) * TILE + tid);
+        }
         if (mask_invalid && more) ridx_next = list_index<EXTRA>(lv, lv.begin + (t + 1) * TILE + row);
         // Is this thread's row masked (beyond the range, or an invalid entry under masking rules)?
         bool masked = true;
@@ -1034,8 +1130,9 @@ sm100_attn_kernel(const AttnParams p) {
           }
         }
         const bool any_masked = __any_sync(0xffffffffu, masked);
+        if (tid == 0) TSTAMP(t, 23);
 
-        if (ok && !mbar_wait_warp(bar_s_full, t & 1, lane)) { atomicExch(&g_attn_error, ERR_SFULL); ok = false; }
+        if (ok && !mbar_wait(bar_s_full, t & 1)) { atomicExch(&g_attn_error, ERR_SFULL); ok = false; }
         tc_fence_after_sync();
         if (tid == 0) TSTAMP(t, 3);
 
@@ -1069,56 +1166,10 @@ sm100_attn_kernel(const AttnParams p) {
         const float ymax = load_scores(true);
         // Does any score of the tile exceed its reference by more than the threshold?
         if (bar_red_or(WORKER_BARRIER, WORKERS, ymax > RESCALE_THRESHOLD)) {
-          // Raise the references: column maxima over the tile's rows, new reference where
-          // the maximum has grown by more than the threshold (also the first finite one),
-          // O^T and the denominators scaled down to it.
-          {
-            uint32_t s[CPW];
-            tmem_ld_cols<CPW>(tmem + tlane + COL_S + cg * CPW, s);
-            tmem_ld_wait();
-            uint32_t pk[CPW / 2];
-#pragma unroll
-            for (int i = 0; i < CPW / 2; ++i) {
-              const float a = masked ? -INFINITY : __uint_as_float(s[2 * i]);
-              const float b = masked ? -INFINITY : __uint_as_float(s[2 * i + 1]);
-              pk[i] = pack_bf16x2(a, b);
-            }
-            const float cm = warp_col_max_packed<CPW>(pk, lane);
-            if (lane < CPW) ctrl.wred[lg][cg * CPW + lane] = cm;
-          }
-          if (tid == 0) ctrl.resc = 0;
-          bar_sync(WORKER_BARRIER, WORKERS);
-          if (tid < NH) {
-            const float tm = fmaxf(fmaxf(ctrl.wred[0][tid], ctrl.wred[1][tid]),
-                                   fmaxf(ctrl.wred[2][tid], ctrl.wred[3][tid])) * cs;
-            const float mr = ctrl.mref[tid];
-            float alpha = 1.f;
-            if (tm > mr + RESCALE_THRESHOLD) {
-              alpha = (mr <= NEG_HUGE) ? 0.f : ex2(mr - tm);
-              ctrl.mref[tid] = tm;
-              ctrl.resc = 1;
-            }
-            ctrl.alpha[tid] = alpha;
-          }
-          bar_sync(WORKER_BARRIER, WORKERS);
+          raise_references<NH>(ctrl, tmem + tlane, masked, cs, t > 0);
           if (ctrl.resc) {
 #pragma unroll
             for (int i = 0; i < CPW; ++i) lsum[i] *= ctrl.alpha[cg * CPW + i];
-            if (t > 0) {
-              // this warp rescales slice cg of O^T for its 32 TMEM lanes
-#pragma unroll 1
-              for (int c4 = 0; c4 < NH / 16; ++c4) {
-                uint32_t o[16];
-                const uint32_t addr = tmem + tlane + COL_O + cg * O_SLICE_COLS + c4 * 16;
-                tmem_ld16(addr, o);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                  o[i] = __float_as_uint(__uint_as_float(o[i]) * ctrl.alpha[c4 * 16 + i]);
-                tmem_st16(addr, o);
-              }
-              tmem_st_wait();
-            }
           }
           // (alpha / resc are rewritten only behind the next tile's barrier, which every
           // worker reaches after it has read them here)
@@ -1158,17 +1209,24 @@ sm100_attn_kernel(const AttnParams p) {
 
       // fill tile t + 1 (behind the P.V product of tile t, if there is one)
       if (more) {
+        advance_loads(ld_tile);
         if constexpr (S::PAGED) {
           // registers hold tile t + 1 (scales sw_cur); they are refilled with tile t + 2
-          advance_loads(ld_tile);                       // rows of tile t + 2 from e_ld
-          fetch_entries(ld_tile + 1);
           fill(t, ld_tile < n_tiles);
+#ifdef EXP_BURST
+          if (ld_tile < n_tiles) {
+            static_for<0, S::LINES>([&](auto lc) {
+              constexpr int line = decltype(lc)::value;
+#pragma unroll
+              for (int hh = 0; hh < 2; ++hh) load_line<FMT, DQK, line>(stage.d[hh][line], row_ld[hh], geo);
+            });
+          }
+#endif
+          if (tid == 0) TSTAMP(t + 1, 7);
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) sw_cur[hh] = sw_ld[hh];
         } else {
-          advance_loads(ld_tile);                       // rows of tile t + 1 from e_ld
-          fetch_entries(ld_tile + 1);
-          fill(t, true);
+          fill(t, true);                                // rows of tile t + 1
         }
         if (tid == 0) TSTAMP(t + 1, 0);
       }
@@ -1194,7 +1252,7 @@ sm100_attn_kernel(const AttnParams p) {
   grid_launch_dependents();
 
   // ---- final denominators and output factors ---------------------------------------
-  if (ok && !mbar_wait_warp(bar_o_done, 0, lane)) { atomicExch(&g_attn_error, ERR_ODONE); ok = false; }
+  if (ok && !mbar_wait(bar_o_done, 0)) { atomicExch(&g_attn_error, ERR_ODONE); ok = false; }
   tc_fence_after_sync();
   if (tid == 0) stamp(p, 3);
   if (tid == 0) stamp_cta(p, 2);
@@ -1273,7 +1331,6 @@ sm100_attn_kernel(const AttnParams p) {
   if (tid == 0) stamp(p, 5);
   if (tid == 0) stamp_cta(p, 3);
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
-  (void)e_first;
 }
 
 // The dynamic shared-memory limit of a kernel is a per-device attribute: set once per

@@ -296,8 +296,8 @@ int dsv4_device_info(int device, int* major, int* minor, int* num_sms);
 int dsv4_device_status(int32_t* status_out, int reset);
 
 /* Debug aid: give the attention kernels a device buffer of at least
- * 256 + 4 * (CTAs of the largest launch) int64.  CTA (0,0,0) of every later launch
- * writes SM cycle-counter stamps of its pipeline stages into the first 256 slots and
+ * 1024 + 4 * (CTAs of the largest launch) int64.  CTA (0,0,0) of every later launch
+ * writes SM cycle-counter stamps of its pipeline stages into the first 1024 slots and
  * every CTA four global-timer stamps (start, set-up done, last product done, end)
  * behind them (null switches it off).  Process-wide; not for production.  The stamps
  * exist only in a library built with -DDSV4_TIMELINE; otherwise this is a no-op.     */
