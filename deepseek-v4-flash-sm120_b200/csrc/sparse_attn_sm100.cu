@@ -432,14 +432,10 @@ __device__ __forceinline__ void store_line(const uint4& v, uint32_t sK, int row,
       const ScalePair c = scale_pair(scale_byte_of<FMT, LINE>(sw, piece));
       const uint32_t a = rbase + (ci >> 2) * KBLOCK_BYTES + (((2 * (ci & 3)) ^ x) << 4);
       uint32_t o[8];
-#ifdef EXP_NOCONV
-      o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w; o[4] = v.x ^ c.c1; o[5] = v.y; o[6] = v.z; o[7] = v.w ^ c.c2;
-#else
       dequant4(v.x, c, o[0], o[1]);
       dequant4(v.y, c, o[2], o[3]);
       dequant4(v.z, c, o[4], o[5]);
       dequant4(v.w, c, o[6], o[7]);
-#endif
       st_shared_v4(a, o[0], o[1], o[2], o[3]);
       st_shared_v4(a ^ 16, o[4], o[5], o[6], o[7]);             // the neighbouring chunk
     } else if (ci < S::CH) {
@@ -1039,16 +1035,8 @@ sm100_attn_kernel(const AttnParams p) {
               store_line<FMT, DQK, line>(stage.d[hh][line], sK, geo.row(hh), geo, sw_cur[hh]);
             }
           });
-          if (tid == 0 && g == 1) TSTAMP(wait_tile + 1, 24);
-#ifdef DSV4_TIMELINE
-          if (g == 1) {
-            fence_async_smem();
-            if (tid == 0) TSTAMP(wait_tile + 1, 25);
-          }
-#endif
-          publish(g);
-          if (tid == 0) TSTAMP(wait_tile + 1, 9 + 2 * g);
-#if !defined(EXP_BURST) && !defined(EXP_NOLOAD)
+          // the requests for the same lines of the tile after next go out before the proxy
+          // fence: issuing them takes as long as the stores above need to drain
           if (load_next) {
             static_for<L0, L1 + 1>([&](auto lc) {
               constexpr int line = decltype(lc)::value;
@@ -1056,8 +1044,8 @@ sm100_attn_kernel(const AttnParams p) {
               for (int hh = 0; hh < 2; ++hh) load_line<FMT, DQK, line>(stage.d[hh][line], row_ld[hh], geo);
             });
           }
-#endif
-          if (tid == 0 && g == 1) TSTAMP(wait_tile + 1, 27);
+          publish(g);
+          if (tid == 0) TSTAMP(wait_tile + 1, 9 + 2 * g);
         } else {
           static_for<L0, L1 + 1>([&](auto lc) {
             constexpr int line = decltype(lc)::value;
@@ -1213,15 +1201,6 @@ sm100_attn_kernel(const AttnParams p) {
         if constexpr (S::PAGED) {
           // registers hold tile t + 1 (scales sw_cur); they are refilled with tile t + 2
           fill(t, ld_tile < n_tiles);
-#ifdef EXP_BURST
-          if (ld_tile < n_tiles) {
-            static_for<0, S::LINES>([&](auto lc) {
-              constexpr int line = decltype(lc)::value;
-#pragma unroll
-              for (int hh = 0; hh < 2; ++hh) load_line<FMT, DQK, line>(stage.d[hh][line], row_ld[hh], geo);
-            });
-          }
-#endif
           if (tid == 0) TSTAMP(t + 1, 7);
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) sw_cur[hh] = sw_ld[hh];
