@@ -247,70 +247,95 @@ combine_kernel(Dsv4CombineArgs a) {
 }
 
 // ---------------------------------------------------------------------------
-// KV store / quantise: one warp per token.  Lane l owns 16 consecutive latent
-// values (14 or 16 per lane... see below), tile amax by shuffles, e4m3 by the
-// hardware saturating convert.
+// KV store / quantise.  HBM-bound: per token d_nope * 2 + 128 bytes in, 644 / 584 bytes out.
+// A warp handles STORE_TOKENS tokens at a time: lane l owns 16 consecutive latent values of
+// each, and all of the warp's loads (two 16-byte loads per lane and token, plus the RoPE
+// rows) are in flight before the first value is looked at.  Tile amax by shuffles, e4m3 by
+// the hardware saturating convert.
 // ---------------------------------------------------------------------------
+constexpr int STORE_TOKENS = 4;          // tokens in flight per warp
+constexpr int STORE_WARPS = 8;
+
 template <int FMT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(STORE_WARPS * 32)
 kv_store_kernel(Dsv4StoreArgs a) {
   using T = KvTraits<FMT>;
   constexpr int PER_LANE = 16;                      // 32 lanes x 16 = 512 >= D_NOPE
   constexpr int LANES_PER_TILE = T::TILE / PER_LANE;
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (warp >= a.n_tokens) return;
-  const int64_t slot = a.slots[warp];
-  if (slot < 0 || slot >= static_cast<int64_t>(a.num_blocks) * a.page_block_size) return;
-  const int page = static_cast<int>(slot / a.page_block_size);
-  const int r = static_cast<int>(slot - static_cast<int64_t>(page) * a.page_block_size);
-  uint8_t* base = reinterpret_cast<uint8_t*>(a.kv) + static_cast<int64_t>(page) * a.stride_kv_block;
-  uint8_t* row = base + static_cast<int64_t>(r) * T::ROW_BYTES;
-  uint8_t* scl = base + static_cast<int64_t>(a.page_block_size) * T::ROW_BYTES + r * T::SLOTS;
-
+  grid_dependency_wait();                           // the rows may come from the kernel before
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int tok0 = warp * STORE_TOKENS;
   const bool active = lane * PER_LANE < T::D_NOPE;
-  const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(a.k_nope) +
-                             static_cast<int64_t>(warp) * a.stride_nope + lane * PER_LANE;
-  float x[PER_LANE];
-  float amax = 0.f;
-  if (active) {
-    uint4 v0 = *reinterpret_cast<const uint4*>(src);
-    uint4 v1 = *reinterpret_cast<const uint4*>(src + 8);
-    uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+  const int64_t n_slots = static_cast<int64_t>(a.num_blocks) * a.page_block_size;
+
+  int64_t slot[STORE_TOKENS];
+  uint4 v[STORE_TOKENS][2], rope[STORE_TOKENS];
+#pragma unroll
+  for (int k = 0; k < STORE_TOKENS; ++k) {
+    const int tok = tok0 + k;
+    slot[k] = tok < a.n_tokens ? a.slots[tok] : -1;
+    v[k][0] = v[k][1] = rope[k] = make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int k = 0; k < STORE_TOKENS; ++k) {
+    if (slot[k] < 0 || slot[k] >= n_slots) continue;
+    const int tok = tok0 + k;
+    if (active) {
+      const uint4* src = reinterpret_cast<const uint4*>(
+          reinterpret_cast<const __nv_bfloat16*>(a.k_nope) + static_cast<int64_t>(tok) * a.stride_nope +
+          lane * PER_LANE);
+      v[k][0] = __ldg(src);
+      v[k][1] = __ldg(src + 1);
+    }
+    if (lane < 8)   // RoPE: 64 BF16 = 128 B = 8 x 16 B
+      rope[k] = __ldg(reinterpret_cast<const uint4*>(
+                          reinterpret_cast<const __nv_bfloat16*>(a.k_rope) +
+                          static_cast<int64_t>(tok) * a.stride_rope) + lane);
+  }
+#pragma unroll
+  for (int k = 0; k < STORE_TOKENS; ++k) {
+    if (slot[k] < 0 || slot[k] >= n_slots) continue;         // warp-uniform
+    const int page = static_cast<int>(slot[k] / a.page_block_size);
+    const int r = static_cast<int>(slot[k] - static_cast<int64_t>(page) * a.page_block_size);
+    uint8_t* base = reinterpret_cast<uint8_t*>(a.kv) + static_cast<int64_t>(page) * a.stride_kv_block;
+    uint8_t* row = base + static_cast<int64_t>(r) * T::ROW_BYTES;
+    uint8_t* scl = base + static_cast<int64_t>(a.page_block_size) * T::ROW_BYTES + r * T::SLOTS;
+    const uint32_t w[8] = {v[k][0].x, v[k][0].y, v[k][0].z, v[k][0].w,
+                           v[k][1].x, v[k][1].y, v[k][1].z, v[k][1].w};
+    float x[PER_LANE];
+    float amax = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       x[2 * i] = __uint_as_float(w[i] << 16);
       x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
       amax = fmaxf(amax, fmaxf(fabsf(x[2 * i]), fabsf(x[2 * i + 1])));
     }
-  }
 #pragma unroll
-  for (int o = 1; o < LANES_PER_TILE; o <<= 1)
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  // e = ceil(log2(max(amax, 1e-4) / 448)) from the fp32 exponent field.
-  const float rr = fmaxf(amax, 1e-4f) / 448.0f;
-  const uint32_t rb = __float_as_uint(rr);
-  int e = static_cast<int>(rb >> 23) - 127 + ((rb & 0x7fffffu) ? 1 : 0);
-  const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);   // 2^-e, |e| small
-  if (active) {
-    uint32_t packed[4];
+    for (int o = 1; o < LANES_PER_TILE; o <<= 1)
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    // e = ceil(log2(max(amax, 1e-4) / 448)) from the fp32 exponent field.
+    const float rr = fmaxf(amax, 1e-4f) / 448.0f;
+    const uint32_t rb = __float_as_uint(rr);
+    const int e = static_cast<int>(rb >> 23) - 127 + ((rb & 0x7fffffu) ? 1 : 0);
+    const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);   // 2^-e, |e| small
+    if (active) {
+      uint32_t packed[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint16_t a01 = __nv_cvt_float2_to_fp8x2(make_float2(x[4 * i] * inv, x[4 * i + 1] * inv),
-                                              __NV_SATFINITE, __NV_E4M3);
-      uint16_t a23 = __nv_cvt_float2_to_fp8x2(make_float2(x[4 * i + 2] * inv, x[4 * i + 3] * inv),
-                                              __NV_SATFINITE, __NV_E4M3);
-      packed[i] = static_cast<uint32_t>(a01) | (static_cast<uint32_t>(a23) << 16);
+      for (int i = 0; i < 4; ++i) {
+        const uint16_t a01 = __nv_cvt_float2_to_fp8x2(make_float2(x[4 * i] * inv, x[4 * i + 1] * inv),
+                                                      __NV_SATFINITE, __NV_E4M3);
+        const uint16_t a23 = __nv_cvt_float2_to_fp8x2(make_float2(x[4 * i + 2] * inv, x[4 * i + 3] * inv),
+                                                      __NV_SATFINITE, __NV_E4M3);
+        packed[i] = static_cast<uint32_t>(a01) | (static_cast<uint32_t>(a23) << 16);
+      }
+      *reinterpret_cast<uint4*>(row + lane * PER_LANE) =
+          make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      if (lane % LANES_PER_TILE == 0) scl[lane / LANES_PER_TILE] = static_cast<uint8_t>(e + 127);
     }
-    *reinterpret_cast<uint4*>(row + lane * PER_LANE) =
-        make_uint4(packed[0], packed[1], packed[2], packed[3]);
-    if (lane % LANES_PER_TILE == 0) scl[lane / LANES_PER_TILE] = static_cast<uint8_t>(e + 127);
-  }
-  if (lane >= 32 - (T::SLOTS - T::N_SCALE) && T::SLOTS > T::N_SCALE)
-    scl[T::N_SCALE + (31 - lane)] = 0;
-  if (lane < 8) {   // RoPE: 64 BF16 = 128 B = 8 x 16 B
-    const uint4* rs = reinterpret_cast<const uint4*>(
-        reinterpret_cast<const __nv_bfloat16*>(a.k_rope) + static_cast<int64_t>(warp) * a.stride_rope);
-    *reinterpret_cast<uint4*>(row + T::D_NOPE + lane * 16) = rs[lane];
+    if (lane >= 32 - (T::SLOTS - T::N_SCALE) && T::SLOTS > T::N_SCALE)
+      scl[T::N_SCALE + (31 - lane)] = 0;
+    if (lane < 8) *reinterpret_cast<uint4*>(row + T::D_NOPE + lane * 16) = rope[k];
   }
 }
 
@@ -385,10 +410,16 @@ int combine_max_splits() { return COMBINE_MAX_SPLITS; }
 
 cudaError_t launch_kv_store(const Dsv4StoreArgs& a, cudaStream_t st) {
   if (a.n_tokens <= 0) return cudaSuccess;
-  const int blocks = (a.n_tokens + 7) / 8;
-  if (a.kv_format == DSV4_KV_MODEL1) kv_store_kernel<DSV4_KV_MODEL1><<<blocks, 256, 0, st>>>(a);
-  else kv_store_kernel<DSV4_KV_V32><<<blocks, 256, 0, st>>>(a);
-  return cudaGetLastError();
+  constexpr int PER_BLOCK = STORE_WARPS * STORE_TOKENS;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((a.n_tokens + PER_BLOCK - 1) / PER_BLOCK);
+  cfg.blockDim = dim3(STORE_WARPS * 32);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  cfg.attrs = attr;
+  cfg.numAttrs = add_overlap_attribute(attr);
+  return a.kv_format == DSV4_KV_MODEL1 ? cudaLaunchKernelEx(&cfg, kv_store_kernel<DSV4_KV_MODEL1>, a)
+                                       : cudaLaunchKernelEx(&cfg, kv_store_kernel<DSV4_KV_V32>, a);
 }
 
 cudaError_t launch_gather_dequant(const void* kv, int64_t stride, int kv_format, int num_blocks,
