@@ -498,8 +498,9 @@ def run_ours(args):
 
     more = {}
     if not args.no_more:
-        more.update(run_more(dev, K, ops, W, stream, rank, world, barrier, max_over_ranks,
-                             hbm_peak, tf_peak))
+        if not args.head_tp_only:
+            more.update(run_more(dev, K, ops, W, stream, rank, world, barrier, max_over_ranks,
+                                 hbm_peak, tf_peak))
         if world > 1:
             more.update(run_head_tp(dev, K, ops, W, stream, rank, world, max_over_ranks))
     extras = {}
@@ -651,10 +652,24 @@ def run_head_tp(dev, K, ops, W, stream, rank, world, max_over_ranks):
             call.decode(stream.cuda_stream)
             return p2p.gather(call.out, lse_loc, stream.cuda_stream)
 
+        def step_fused(i, _gather=True):
+            call.set_indices(wl.indices[i % ns])
+            return p2p.decode_gather(call, stream.cuda_stream)
+
+        # the floor of any exchange built on flags in peer memory: no rows, flags only
+        flags_only = sharding.HeadGather(0, 1, wl.q.size(2), dev)
+
+        def step_flags(i, _gather=True):
+            call.set_indices(wl.indices[i % ns])
+            call.decode(stream.cuda_stream)
+            return flags_only.gather(call.out, lse_loc, stream.cuda_stream)
+
         res = {}
         for label, gather in (("decode_plus_nccl_all_gather", True), ("decode_only", False),
-                              ("decode_plus_peer_memory_gather", None)):
-            fn = step_p2p if gather is None else step
+                              ("decode_plus_peer_memory_gather", None),
+                              ("decode_and_exchange_in_one_call", "fused"),
+                              ("decode_plus_flag_barrier_without_rows", "flags")):
+            fn = {"fused": step_fused, "flags": step_flags, None: step_p2p}.get(gather, step)
             n_tp = 1000                                 # >= 50 ms per region at 50 us per step
             for i in range(5):
                 fn(i, gather)
@@ -833,6 +848,8 @@ def main():
     ap.add_argument("--no-more", action="store_true",
                     help="headline only: skip the target shape, the strong-scaling decode, prefill "
                          "and the head-sharded step")
+    ap.add_argument("--head-tp-only", action="store_true",
+                    help="of the additional measurements keep only the head-sharded step (N >= 2)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--clock-window", type=float, default=1.0,
                     help="seconds of identical untimed load around the timed region over which "

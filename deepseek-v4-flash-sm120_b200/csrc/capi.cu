@@ -375,6 +375,33 @@ int dsv4_gather_heads(const Dsv4GatherArgs* a, void* stream) {
   return e ? cuda_fail(e) : DSV4_OK;
 }
 
+int dsv4_sparse_decode_gather(const Dsv4DecodeArgs* d, const Dsv4GatherArgs* g, void* stream) {
+  if (!d || !g || !g->counter || !g->status || !d->out || !d->lse) return DSV4_ERR_NULL;
+  if (g->world < 1 || g->world > DSV4_MAX_PEERS || g->rank < 0 || g->rank >= g->world ||
+      g->b != d->b || g->s_q != d->s_q || g->h_local != d->h_q)
+    return DSV4_ERR_SHAPE;
+  for (int r = 0; r < g->world; ++r) {
+    if (!g->peer_out[r] || !g->peer_lse[r] || !g->peer_flags[r]) return DSV4_ERR_NULL;
+    if (!aligned16(g->peer_out[r])) return DSV4_ERR_ALIGN;
+  }
+  // the local result must be dense: it is what the exchange kernel reads
+  if (d->stride_o_h != 512 || d->stride_o_s != static_cast<int64_t>(d->h_q) * 512 ||
+      d->stride_o_b != static_cast<int64_t>(d->s_q) * d->h_q * 512 || d->stride_lse_s != 1 ||
+      d->stride_lse_h != d->s_q || d->stride_lse_b != static_cast<int64_t>(d->h_q) * d->s_q)
+    return DSV4_ERR_LAYOUT;
+  // Decode (with its split combine, when the plan has one) and the exchange kernel behind it
+  // with programmatic dependent launch: the exchange kernel is resident before the rows are
+  // final.  A combine step that stored straight into the peers' buffers was measured 1-2 us
+  // slower per step than this pair (more CTAs fencing at system scope, narrower NVLink
+  // stores), so it was taken out again.
+  int rc = dsv4_sparse_decode(d, stream);
+  if (rc) return rc;
+  Dsv4GatherArgs ga = *g;
+  ga.out_local = d->out;
+  ga.lse_local = d->lse;
+  return dsv4_gather_heads(&ga, stream);
+}
+
 int dsv4_umma_selftest(int mode, int n, int k, const void* a, const void* b, float* d,
                        int32_t* status, void* stream) {
   if (!a || !b || !d || !status) return DSV4_ERR_NULL;

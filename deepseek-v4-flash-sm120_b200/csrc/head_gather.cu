@@ -25,7 +25,7 @@ namespace dsv4 {
 namespace {
 
 constexpr int GATHER_THREADS = 256;
-constexpr long long GATHER_SPINS = 1ll << 21;     // x >= 100 ns: a few hundred ms at most
+constexpr unsigned long long GATHER_WAIT_NS = 300000000ull;    // bounded wait for the peers' flags
 
 __device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -34,6 +34,32 @@ __device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
   int32_t v;
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
+}
+
+// The flag exchange that ends a step, run by the last CTA of the grid: this rank's slot of
+// every rank's flag array gets the step number (release, system scope), then the CTA waits,
+// bounded, until every slot of the local array has reached it.
+__device__ __forceinline__ void publish_and_wait(const Dsv4GatherArgs& a) {
+  if (threadIdx.x < a.world) {
+    st_release_sys(a.peer_flags[threadIdx.x] + a.rank, a.step);
+    const int32_t* mine = a.peer_flags[a.rank] + threadIdx.x;
+    // The flags live in this GPU's own memory, so polling them costs no NVLink traffic; no
+    // pause between probes (a paused thread was measured to notice a change 0.5-0.9 us
+    // late).  Bounded by wall-clock time: about 0.3 s.
+    long long spins = 0;
+    unsigned long long t0 = 0;
+    while (ld_acquire_sys(mine) - a.step < 0) {     // wrap-safe comparison
+      if ((++spins & 1023) == 0) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > GATHER_WAIT_NS) {
+          atomicExch(a.status, 1 + static_cast<int>(threadIdx.x));
+          break;
+        }
+      }
+    }
+  }
 }
 
 __global__ void __launch_bounds__(GATHER_THREADS)
@@ -64,32 +90,26 @@ gather_heads_kernel(const Dsv4GatherArgs a) {
     const int64_t dst = bi * h_q * a.s_q + static_cast<int64_t>(rank) * a.h_local * a.s_q + r;
     for (int p = 0; p < world; ++p) a.peer_lse[p][dst] = v;
   }
-  __threadfence_system();
+  // One system-scope fence per CTA, after the CTA's barrier: the barrier orders every thread's
+  // peer stores before the fence, and the fence is cumulative.  (A fence per thread made each
+  // of the grid's 32 K threads wait for a round trip over NVLink.)
   __syncthreads();
   __shared__ int s_last;
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const unsigned int done = atomicAdd(reinterpret_cast<unsigned int*>(a.counter), 1u);
     s_last = (done + 1u) == gridDim.x;
     // The last CTA puts the counter back to zero, so the next call may use another grid
     // (the grid follows the batch size).  Calls that share a counter are ordered by the
     // stream, and no CTA of this launch touches the counter after its own increment.
-    if (s_last) *reinterpret_cast<volatile unsigned int*>(a.counter) = 0u;
+    if (s_last) {
+      *reinterpret_cast<volatile unsigned int*>(a.counter) = 0u;
+      __threadfence();                    // the other CTAs' increments happen before the flags
+    }
   }
   __syncthreads();
   if (!s_last) return;
-  if (threadIdx.x < world) {
-    __threadfence_system();
-    st_release_sys(a.peer_flags[threadIdx.x] + rank, a.step);
-    const int32_t* mine = a.peer_flags[rank] + threadIdx.x;
-    long long spins = 0;
-    while (ld_acquire_sys(mine) - a.step < 0) {     // wrap-safe comparison
-      if (++spins > GATHER_SPINS) {
-        atomicExch(a.status, 1 + static_cast<int>(threadIdx.x));
-        break;
-      }
-      __nanosleep(100);
-    }
-  }
+  publish_and_wait(a);
 }
 
 }  // namespace

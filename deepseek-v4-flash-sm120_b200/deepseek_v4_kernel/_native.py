@@ -73,6 +73,7 @@ SYMBOLS = {
                                    C.POINTER(C.c_int)]),
     "dsv4_plan_splits": (C.c_int, [C.c_int] * 6),
     "dsv4_gather_heads": (C.c_int, [C.POINTER(GatherArgs), C.c_void_p]),
+    "dsv4_sparse_decode_gather": (C.c_int, [C.POINTER(DecodeArgs), C.POINTER(GatherArgs), C.c_void_p]),
     "dsv4_decode_partial_sets": (C.c_int, [C.POINTER(DecodeArgs)]),
     "dsv4_sparse_decode": (C.c_int, [C.POINTER(DecodeArgs), vp]),
     "dsv4_sparse_decode_noalloc": (C.c_int, [C.POINTER(DecodeArgs), vp]),

@@ -148,6 +148,22 @@ class HeadGather:
             self._N.check(rc, "dsv4_gather_heads")
         return self.views[k]
 
+    def decode_gather(self, call, stream: int):
+        """Decode this rank's head shard with the prepared launch `call` (a cuda.DecodeCall
+        over h_q / world heads) and exchange the result in the same call
+        (`dsv4_sparse_decode_gather`): the exchange kernel is queued behind the decode with
+        programmatic dependent launch.  Returns (out, lse) views like `gather`."""
+        if not hasattr(self, "_args"):
+            self._args = [self._args_for(0), self._args_for(1)]
+        self.step += 1
+        k = self.step & 1
+        a = self._args[k]
+        a.step = self.step
+        rc = self._N.lib.dsv4_sparse_decode_gather(self._C.byref(call.args), self._C.byref(a), stream)
+        if rc:
+            self._N.check(rc, "dsv4_sparse_decode_gather")
+        return self.views[k]
+
     def timed_out(self) -> bool:
         """True when a bounded wait for a peer's shard ran out (synchronises)."""
         return bool(self.status.item() != 0)

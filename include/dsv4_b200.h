@@ -196,6 +196,17 @@ typedef struct Dsv4GatherArgs {
 
 int dsv4_gather_heads(const Dsv4GatherArgs* args, void* cuda_stream);
 
+/* Head-sharded decode and its exchange in one call: decode this rank's h_q heads
+ * (decode->h_q == gather->h_local) into decode->out / decode->lse, which must be dense, and
+ * leave the result of ALL ranks' heads in every rank's gathered buffers.  The exchange
+ * kernel of dsv4_gather_heads is queued behind the decode with programmatic dependent
+ * launch, so it is resident on the GPU before the rows are final; it reads the rows once
+ * and stores them to every rank with 16-byte peer stores (no multicast, no TMA).
+ * gather->out_local / lse_local are ignored.  Same step / buffer-set rules as
+ * dsv4_gather_heads.  No reference counterpart (the reference has no multi-GPU code).    */
+int dsv4_sparse_decode_gather(const Dsv4DecodeArgs* decode, const Dsv4GatherArgs* gather,
+                              void* cuda_stream);
+
 /* ---------------------------------------------------------------------------
  * Split-KV combine alone: replaces dsv4_split_kv_combine
  * (csrc/sm120/decode/split_kv_combine.cuh:23-110).

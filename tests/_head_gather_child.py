@@ -42,6 +42,17 @@ def main():
         assert torch.equal(g_out, n_out) and torch.equal(g_lse, n_lse), f"step {step}: differs from NCCL"
         torch.testing.assert_close(g_out.float(), full_out.float(), atol=5e-3, rtol=5e-3)
         torch.testing.assert_close(g_lse, full_lse, atol=1e-3, rtol=1e-3)
+        # decode and exchange in one call, for split plans with and without a combine step:
+        # bit-identical to an all-gather of the same call's own local result
+        for n_splits in (1, 3, 8):
+            call = K.DecodeCall(qd[:, :, hs].contiguous(), kv4, idx_s, sm, n_splits=n_splits)
+            f_out, f_lse = gather.decode_gather(call, stream)
+            torch.cuda.synchronize(dev)
+            assert not gather.timed_out(), "a peer's shard did not arrive (one-call path)"
+            r_out, r_lse = sharding.all_gather_heads(call.out, call.lse)
+            assert torch.equal(f_out, r_out) and torch.equal(f_lse, r_lse), "one-call path differs from NCCL"
+            torch.testing.assert_close(f_out.float(), full_out.float(), atol=5e-3, rtol=5e-3)
+            torch.testing.assert_close(f_lse, full_lse, atol=1e-3, rtol=1e-3)
     assert K.device_status() == 0
     dist.barrier()
     dist.destroy_process_group()

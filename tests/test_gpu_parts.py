@@ -169,3 +169,38 @@ def test_head_gather_counter_survives_a_change_of_grid(K):
         torch.cuda.synchronize()
         assert status.item() == 0 and flags.item() == step and counter.item() == 0
         assert torch.equal(gathered, out_local) and torch.equal(lse_g, lse_local)
+
+
+@pytest.mark.parametrize("n_splits", [1, 2, 5, 16])
+def test_decode_and_exchange_in_one_call_on_one_rank(K, n_splits):
+    """dsv4_sparse_decode_gather with a group of one rank (its "peer" buffers are local):
+    whatever the split plan, the gathered buffers must hold what the plain decode returns,
+    the step flag must be published once, and the shared counter must be back at zero."""
+    import ctypes as C
+    import math
+    import test_gpu_decode as T
+    from deepseek_v4_kernel import _native as N
+    dev = torch.device("cuda", 0)
+    b, h = 5, 16
+    q, pages, idx = T.fake_batch(b, h, 16, 700, seed=31, layout=O.V32)
+    sm = 1.0 / math.sqrt(576)
+    kv4 = pages.to(dev).view(pages.size(0), 64, 1, O.V32.bytes_per_token)
+    sink = torch.randn(h, generator=torch.Generator().manual_seed(2)).to(dev)
+    call = K.DecodeCall(q.to(dev), kv4, idx.to(dev), sm, attn_sink=sink, n_splits=n_splits)
+    stream = torch.cuda.current_stream().cuda_stream
+    call.decode(stream)
+    want_out, want_lse = call.out.clone(), call.lse.clone()
+    gathered = torch.zeros(b, 1, h, 512, dtype=torch.bfloat16, device=dev)
+    lse_g = torch.zeros(b, h, 1, device=dev)
+    flags = torch.zeros(1, dtype=torch.int32, device=dev)
+    counter = torch.zeros(1, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    a = N.GatherArgs()
+    a.world, a.rank, a.b, a.s_q, a.h_local, a.step = 1, 0, b, 1, h, 7
+    a.peer_out[0], a.peer_lse[0], a.peer_flags[0] = gathered.data_ptr(), lse_g.data_ptr(), flags.data_ptr()
+    a.counter, a.status = counter.data_ptr(), status.data_ptr()
+    N.check(N.lib.dsv4_sparse_decode_gather(C.byref(call.args), C.byref(a), stream), "decode_gather")
+    torch.cuda.synchronize()
+    assert K.device_status() == 0 and status.item() == 0
+    assert flags.item() == 7 and counter.item() == 0
+    assert torch.equal(gathered, want_out) and torch.equal(lse_g, want_lse)
