@@ -328,7 +328,29 @@ int dsv4_kv_store(const Dsv4StoreArgs* a, void* stream) {
   if (rc) return rc;
   if (!aligned16(a->k_nope) || !aligned16(a->k_rope) || (a->stride_nope & 7) || (a->stride_rope & 7))
     return DSV4_ERR_ALIGN;
-  cudaError_t e = dsv4::launch_kv_store(*a, static_cast<cudaStream_t>(stream));
+  cudaError_t e = dsv4::launch_kv_store(*a, nullptr, static_cast<cudaStream_t>(stream));
+  return e ? cuda_fail(e) : DSV4_OK;
+}
+
+int dsv4_kv_store_rows(const Dsv4StoreRowsArgs* r, void* stream) {
+  if (!r || !r->k || !r->loc || !r->kv) return DSV4_ERR_NULL;
+  if (r->n_tokens < 0 || r->num_blocks < 1 || r->page_block_size < 1) return DSV4_ERR_SHAPE;
+  if (r->kv_format != DSV4_KV_MODEL1 && r->kv_format != DSV4_KV_V32) return DSV4_ERR_LAYOUT;
+  const int d_qk = r->kv_format == DSV4_KV_MODEL1 ? 512 : 576;
+  int rc = check_paged(r->kv_format, d_qk, r->page_block_size, r->stride_kv_block, r->kv);
+  if (rc) return rc;
+  // the RoPE values start d_qk - 64 elements into the row: 896 / 1024 bytes, a multiple of 16
+  if (!aligned16(r->k) || (r->stride_k & 7) || r->stride_k < d_qk) return DSV4_ERR_ALIGN;
+  Dsv4StoreArgs a{};
+  a.n_tokens = r->n_tokens; a.kv_format = r->kv_format;
+  a.num_blocks = r->num_blocks; a.page_block_size = r->page_block_size;
+  a.k_nope = r->k;
+  a.k_rope = static_cast<const uint16_t*>(r->k) + (d_qk - 64);
+  a.stride_nope = a.stride_rope = r->stride_k;
+  a.kv = r->kv; a.stride_kv_block = r->stride_kv_block;
+  a.slots = r->loc_is_int64 ? static_cast<const int64_t*>(r->loc) : nullptr;
+  const int32_t* loc32 = r->loc_is_int64 ? nullptr : static_cast<const int32_t*>(r->loc);
+  cudaError_t e = dsv4::launch_kv_store(a, loc32, static_cast<cudaStream_t>(stream));
   return e ? cuda_fail(e) : DSV4_OK;
 }
 

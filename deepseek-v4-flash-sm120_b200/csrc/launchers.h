@@ -31,7 +31,8 @@ inline int add_overlap_attribute(cudaLaunchAttribute* attr) {
 cudaError_t launch_simple_attn(const AttnParams& p, int kv_format, int d_qk, cudaStream_t st);
 cudaError_t launch_combine(const Dsv4CombineArgs& a, cudaStream_t st);
 int combine_max_splits();
-cudaError_t launch_kv_store(const Dsv4StoreArgs& a, cudaStream_t st);
+// `slots32` non-null: the slot mapping is int32 and a.slots is ignored.
+cudaError_t launch_kv_store(const Dsv4StoreArgs& a, const int32_t* slots32, cudaStream_t st);
 cudaError_t launch_gather_dequant(const void* kv, int64_t stride, int kv_format, int num_blocks,
                                   int page_block, const int32_t* indices, int n, void* rows,
                                   int method, cudaStream_t st);

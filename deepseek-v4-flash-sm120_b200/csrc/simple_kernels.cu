@@ -258,10 +258,11 @@ constexpr int STORE_WARPS = 8;
 
 template <int FMT>
 __global__ void __launch_bounds__(STORE_WARPS * 32)
-kv_store_kernel(Dsv4StoreArgs a) {
+kv_store_kernel(Dsv4StoreArgs a, const int32_t* slots32) {
   using T = KvTraits<FMT>;
   constexpr int PER_LANE = 16;                      // 32 lanes x 16 = 512 >= D_NOPE
   constexpr int LANES_PER_TILE = T::TILE / PER_LANE;
+  grid_launch_dependents();                         // the next kernel may be placed at once
   grid_dependency_wait();                           // the rows may come from the kernel before
   const int lane = threadIdx.x & 31;
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -274,7 +275,7 @@ kv_store_kernel(Dsv4StoreArgs a) {
 #pragma unroll
   for (int k = 0; k < STORE_TOKENS; ++k) {
     const int tok = tok0 + k;
-    slot[k] = tok < a.n_tokens ? a.slots[tok] : -1;
+    slot[k] = tok >= a.n_tokens ? -1 : slots32 ? static_cast<int64_t>(slots32[tok]) : a.slots[tok];
     v[k][0] = v[k][1] = rope[k] = make_uint4(0, 0, 0, 0);
   }
 #pragma unroll
@@ -408,7 +409,7 @@ cudaError_t launch_combine(const Dsv4CombineArgs& a, cudaStream_t st) {
 
 int combine_max_splits() { return COMBINE_MAX_SPLITS; }
 
-cudaError_t launch_kv_store(const Dsv4StoreArgs& a, cudaStream_t st) {
+cudaError_t launch_kv_store(const Dsv4StoreArgs& a, const int32_t* slots32, cudaStream_t st) {
   if (a.n_tokens <= 0) return cudaSuccess;
   constexpr int PER_BLOCK = STORE_WARPS * STORE_TOKENS;
   cudaLaunchConfig_t cfg = {};
@@ -418,8 +419,9 @@ cudaError_t launch_kv_store(const Dsv4StoreArgs& a, cudaStream_t st) {
   cudaLaunchAttribute attr[1];
   cfg.attrs = attr;
   cfg.numAttrs = add_overlap_attribute(attr);
-  return a.kv_format == DSV4_KV_MODEL1 ? cudaLaunchKernelEx(&cfg, kv_store_kernel<DSV4_KV_MODEL1>, a)
-                                       : cudaLaunchKernelEx(&cfg, kv_store_kernel<DSV4_KV_V32>, a);
+  return a.kv_format == DSV4_KV_MODEL1
+             ? cudaLaunchKernelEx(&cfg, kv_store_kernel<DSV4_KV_MODEL1>, a, slots32)
+             : cudaLaunchKernelEx(&cfg, kv_store_kernel<DSV4_KV_V32>, a, slots32);
 }
 
 cudaError_t launch_gather_dequant(const void* kv, int64_t stride, int kv_format, int num_blocks,

@@ -64,6 +64,13 @@ class StoreArgs(C.Structure):
         (n, i64) for n in ("stride_nope", "stride_rope", "stride_kv_block")]
 
 
+class StoreRowsArgs(C.Structure):
+    _fields_ = [(n, i32) for n in ("n_tokens", "kv_format", "num_blocks", "page_block_size")] + [
+        (n, vp) for n in ("k", "loc", "kv")] + [
+        (n, i64) for n in ("stride_k", "stride_kv_block")] + [
+        (n, i32) for n in ("loc_is_int64", "reserved")]
+
+
 # name -> (restype, argtypes); every symbol include/dsv4_b200.h declares.
 SYMBOLS = {
     "dsv4_abi_version": (C.c_int, []),
@@ -80,6 +87,7 @@ SYMBOLS = {
     "dsv4_split_combine": (C.c_int, [C.POINTER(CombineArgs), vp]),
     "dsv4_sparse_prefill": (C.c_int, [C.POINTER(PrefillArgs), vp]),
     "dsv4_kv_store": (C.c_int, [C.POINTER(StoreArgs), vp]),
+    "dsv4_kv_store_rows": (C.c_int, [C.POINTER(StoreRowsArgs), vp]),
     "dsv4_gather_dequant": (C.c_int, [vp, i64, i32, i32, i32, vp, i32, vp, i32, vp]),
     "dsv4_device_status": (C.c_int, [C.POINTER(C.c_int32), C.c_int]),
     "dsv4_debug_set_timeline": (C.c_int, [vp]),

@@ -259,6 +259,33 @@ def kv_store(k_nope, k_rope, slots, kv) -> None:
                 "dsv4_kv_store")
 
 
+def kv_store_rows(k, loc, kv) -> None:
+    """Quantise and store tokens given as the cache writer of the serving framework has
+    them: k [n, d_qk] or [n, 1, d_qk] bf16 (latent values then the 64 RoPE values; any row
+    stride that is a multiple of 8 elements, so a column slice of a wider projection output
+    is taken as it is), loc [n] int32 or int64 cache slots (negative = skip),
+    kv [num_blocks, page_block, 1, 584|644].  Same bytes as `kv_store`."""
+    _require(k.is_cuda and kv.is_cuda and kv.dim() == 4, "k / kv must be CUDA tensors")
+    _require(k.dtype == torch.bfloat16, "k must be bf16")
+    if k.dim() == 3:
+        _require(k.size(1) == 1, "k must be [n, d_qk] or [n, 1, d_qk]")
+        k = k[:, 0]
+    _require(k.dim() == 2 and k.stride(1) == 1, "k rows must be dense")
+    _require(loc.dtype in (torch.int32, torch.int64) and loc.is_contiguous() and loc.numel() == k.size(0),
+             "loc must be contiguous int32/int64 [n]")
+    fmt = _kv_format(k.size(1), kv.size(3))
+    _require(kv.dtype in _KV_DTYPES and kv.stride(1) == kv.size(3) and kv.stride(3) == 1,
+             "kv pages must be dense fp8/uint8/int8")
+    a = N.StoreRowsArgs()
+    a.n_tokens, a.kv_format, a.num_blocks, a.page_block_size = k.size(0), fmt, kv.size(0), kv.size(1)
+    a.k, a.loc, a.kv = k.data_ptr(), loc.data_ptr(), kv.data_ptr()
+    a.stride_k, a.stride_kv_block = (k.stride(0) if k.size(0) > 1 else k.size(1)), kv.stride(0)
+    a.loc_is_int64 = int(loc.dtype == torch.int64)
+    with torch.cuda.device(kv.device):
+        N.check(N.lib.dsv4_kv_store_rows(C.byref(a), torch.cuda.current_stream(kv.device).cuda_stream),
+                "dsv4_kv_store_rows")
+
+
 def gather_dequant(kv, indices, method: int = 0) -> torch.Tensor:
     """Dequantised BF16 rows [n, d_qk] of the tokens named by int32 `indices` [n]."""
     _require(kv.is_cuda and kv.dim() == 4 and indices.dtype == torch.int32, "bad arguments")

@@ -282,6 +282,25 @@ typedef struct Dsv4StoreArgs {
 
 int dsv4_kv_store(const Dsv4StoreArgs* args, void* cuda_stream);
 
+/* The same store for the form the serving framework's cache writer has its operands in
+ * (the step before the path: tests/reference.py:45-58 names quant_k_cache_v4 as the
+ * producer of the bytes the kernels read): one BF16 row per token holding the latent
+ * values followed by the 64 RoPE values, [n_tokens, d_qk] with any row stride that is a
+ * multiple of 8 elements (a view of a wider projection output needs no copy), and the
+ * framework's slot mapping as int32 or int64.  Same arithmetic and bytes as
+ * dsv4_kv_store.  No reference counterpart.                                             */
+typedef struct Dsv4StoreRowsArgs {
+  int32_t n_tokens, kv_format, num_blocks, page_block_size;
+  const void* k;                /* BF16 [n_tokens, d_qk], d_qk = 512 (MODEL1) / 576 (V32) */
+  const void* loc;              /* [n_tokens] cache slots; negative = skip       */
+  void* kv;                     /* paged cache bytes                             */
+  int64_t stride_k, stride_kv_block;                   /* elements, bytes        */
+  int32_t loc_is_int64;         /* 0: loc is int32, 1: loc is int64              */
+  int32_t reserved;
+} Dsv4StoreRowsArgs;
+
+int dsv4_kv_store_rows(const Dsv4StoreRowsArgs* args, void* cuda_stream);
+
 /* ---------------------------------------------------------------------------
  * Gather + dequantise only (checks that row selection and FP8 -> BF16 are
  * bit-exact): rows[i] = dequantised d_qk BF16 values of token indices[i], or

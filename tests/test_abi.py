@@ -39,6 +39,7 @@ def test_struct_layout_matches_the_header():
     assert C.sizeof(N.CombineArgs) == 4 * 4 + 5 * 8 + 6 * 8
     assert C.sizeof(N.PrefillArgs) == 12 * 4 + 8 * 8 + 8 * 8
     assert C.sizeof(N.StoreArgs) == 4 * 4 + 4 * 8 + 3 * 8
+    assert C.sizeof(N.StoreRowsArgs) == 4 * 4 + 3 * 8 + 2 * 8 + 2 * 4
     assert N.DecodeArgs.q.offset == 64 and N.PrefillArgs.q.offset == 48
 
 
@@ -70,6 +71,7 @@ def test_null_and_shape_errors_without_a_gpu():
     assert lib.dsv4_split_combine(C.byref(c), None) == 1
     s = N.StoreArgs()
     assert lib.dsv4_kv_store(C.byref(s), None) == 1
+    assert lib.dsv4_kv_store_rows(C.byref(N.StoreRowsArgs()), None) == 1
     assert lib.dsv4_gather_dequant(None, 0, 1, 1, 64, None, 0, None, 0, None) == 1
     assert lib.dsv4_umma_selftest(0, 64, 64, None, None, None, None, None) == 1
 

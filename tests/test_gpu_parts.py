@@ -75,6 +75,31 @@ def test_kv_store_bit_exact(K, layout):
     assert torch.equal(back[:, layout.d_nope:][slots >= 0], k_rope[slots >= 0])
 
 
+@pytest.mark.parametrize("layout", [O.MODEL1, O.V32], ids=["model1", "v32"])
+@pytest.mark.parametrize("loc_dtype", [torch.int32, torch.int64], ids=["loc32", "loc64"])
+def test_kv_store_rows_writes_the_same_bytes(K, layout, loc_dtype):
+    """The cache-writer form (one strided row per token, int32 / int64 slot mapping) must
+    leave exactly the bytes of the oracle quantiser; a row that does not start on a 16-byte
+    boundary is refused."""
+    gen = torch.Generator().manual_seed(9)
+    n, nb, page = 333, 3, 256
+    d_qk = layout.d_nope + 64
+    wide = (torch.randn(n, 1, d_qk + 40, generator=gen) * torch.logspace(-3, 2, n).view(n, 1, 1)).bfloat16()
+    k = wide[:, :, 8:8 + d_qk]                                  # a view: row stride d_qk + 40, offset 16 B
+    loc = torch.randperm(nb * page, generator=gen)[:n].to(loc_dtype)
+    loc[17] = -1
+    want = torch.full((nb, layout.page_bytes(page)), 0x5C, dtype=torch.uint8)
+    body, scales = O.quantize_rows(k[:, 0, :layout.d_nope].contiguous(), k[:, 0, layout.d_nope:].contiguous(), layout)
+    O.store_rows(want, page, layout, loc.long(), body, scales)
+    kv = torch.full((nb, layout.page_bytes(page)), 0x5C, dtype=torch.uint8, device="cuda")
+    kv4 = kv.view(nb, page, 1, layout.bytes_per_token)
+    wide_d = wide.cuda()
+    K.kv_store_rows(wide_d[:, :, 8:8 + d_qk], loc.cuda(), kv4)
+    assert torch.equal(kv.cpu(), want)
+    with pytest.raises(RuntimeError):
+        K.kv_store_rows(wide_d[:, :, 4:4 + d_qk], loc.cuda(), kv4)      # rows start 8 bytes off a 16-byte line
+
+
 @pytest.mark.parametrize("n_splits,h_q", [(2, 16), (5, 64), (128, 64), (256, 8)])
 @pytest.mark.parametrize("with_sink", [False, True])
 def test_combine_matches_oracle(K, n_splits, h_q, with_sink):
