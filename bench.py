@@ -551,7 +551,7 @@ def run_ours(args):
 def run_more(dev, K, ops, W, stream, rank, world, barrier, max_over_ranks, hbm_peak, tf_peak):
     """The rest of the metric, each in a region of at least MIN_REGION_S: the batch-64 target
     shape and one tensor-parallel shard (per rank), the 128-request mixed-length decode split
-    over the ranks (strong scaling) and sparse prefill with its query rows balanced over
+    over the ranks (strong scaling) and sparse prefill with its query rows balanced (by modelled time) over
     the ranks."""
     from deepseek_v4_kernel import sharding
     out = {}
@@ -602,7 +602,7 @@ def run_more(dev, K, ops, W, stream, rank, world, barrier, max_over_ranks, hbm_p
                               "calls_timed": n, "scaling": "strong"}
     del wl, call
     torch.cuda.empty_cache()
-    # sparse prefill: 8192 causal queries, top-k 2048, FP8 pages; rows balanced by pair count
+    # sparse prefill: 8192 causal queries, top-k 2048, FP8 pages; rows balanced by modelled time
     pw = W.config5(dev, ops.kv_store)
     lo, hi = sharding.balanced_query_blocks(pw.q.size(0), pw.indices.size(1), world)[rank]
     q_l, idx_l = pw.q[lo:hi].contiguous(), pw.indices[lo:hi].contiguous()

@@ -26,10 +26,6 @@ template <> struct KvTraits<DSV4_KV_V32> {
   static constexpr int ROW_BYTES = D_NOPE + 2 * D_ROPE, D_QK = D_NOPE + D_ROPE;
 };
 
-__host__ __device__ inline int kv_d_qk(int fmt_or_dqk_hint, int d_qk) {
-  return fmt_or_dqk_hint == DSV4_KV_MODEL1 ? 512 : fmt_or_dqk_hint == DSV4_KV_V32 ? 576 : d_qk;
-}
-
 // ---------------------------------------------------------------------------
 // Plain conversion: fp8 -> fp32, times 2^(s-127) in fp32, round to BF16.
 // Byte 0 means 2^-127 (a fp32 subnormal), matching 2**(b-127) evaluated in fp32.
@@ -50,69 +46,46 @@ __device__ __forceinline__ float dequant_plain(uint32_t byte, uint32_t s) {
 }
 
 // ---------------------------------------------------------------------------
-// Fast conversion used by the tensor-core kernels.  The e4m3 magnitude bits
-// (eeee.mmm) dropped into a BF16 word at bit 4 read as value * 2^-120, for
-// normals and subnormals alike, so ONE packed BF16 multiply by 2^(120+s-127)
-// both rescales and applies the block scale; the product has at most four
-// significant bits and is therefore exact.  Two e4m3 bytes -> one bf16x2 word.
-// Valid for scale bytes 1..134 in one multiply; others take a second multiply.
+// FP8 e4m3 with a UE8M0 block scale -> BF16, two values per 32-bit word.
 // e4m3 NaN (0x7f/0xff) is not preserved (reads as +-480): a cache written by a
 // saturating cast never holds it.
 // ---------------------------------------------------------------------------
-struct ScaleMul {
-  uint32_t c1;   // bf16x2 multiplier applied first
-  uint32_t c2;   // second multiplier, or 0 when one multiply is enough
-};
-
-__device__ __forceinline__ ScaleMul make_scale_mul(uint32_t s) {
-  ScaleMul m;
-  if (s >= 1 && s <= 134) {
-    uint32_t c = (s + 120u) << 7;           // 2^(s-7)
-    m.c1 = c | (c << 16);
-    m.c2 = 0;
-  } else {
-    uint32_t c = 247u << 7;                 // 2^120
-    uint32_t d = s ? (s << 7) : 0x0040u;    // 2^(s-127); byte 0 -> subnormal 2^-127
-    m.c1 = c | (c << 16);
-    m.c2 = d | (d << 16);
-  }
-  return m;
-}
-
 __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
   uint32_t d;
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
 
-// w holds four e4m3 bytes; returns BF16 pairs (byte0, byte1) and (byte2, byte3).
-__device__ __forceinline__ void dequant4_fast(uint32_t w, const ScaleMul& m, uint32_t& lo,
-                                              uint32_t& hi) {
-  uint32_t t0 = __byte_perm(w, 0u, 0x1404);     // [0, b0, 0, b1]
-  uint32_t t1 = __byte_perm(w, 0u, 0x3424);     // [0, b2, 0, b3]
-  uint32_t x0 = (t0 & 0x80008000u) | ((t0 >> 4) & 0x07F007F0u);
-  uint32_t x1 = (t1 & 0x80008000u) | ((t1 >> 4) & 0x07F007F0u);
-  x0 = bf16x2_mul(x0, m.c1);
-  x1 = bf16x2_mul(x1, m.c1);
-  if (m.c2) {
-    x0 = bf16x2_mul(x0, m.c2);
-    x1 = bf16x2_mul(x1, m.c2);
-  }
-  lo = x0;
-  hi = x1;
+// e4m3 -> BF16 with the block scale.  The byte, sign-extended to 16 bits and shifted left by
+// four, has the e4m3 magnitude bits where a BF16 word reads them as value * 2^-120 (normals
+// and subnormals alike) and the sign in bit 15.  Two packed multiplies then rescale and apply
+// the UE8M0 scale 2^(s-127) for EVERY scale byte, each of them exact (the value has at most
+// four significant bits) unless the result leaves the BF16 range, where the single rounding
+// is the same as that of an fp32 product rounded to BF16:
+//   s <= 127:  c1 = 2^(s-7),  c2 = 1;       s > 127:  c1 = 2^120 (giving the e4m3 value itself),
+//   c2 = 2^(s-127).
+// Branch-free and on the FMA pipe, which the attention kernel leaves idle; its integer pipe is the
+// busy one.  (prmt through inline PTX: __byte_perm drops the selector bit that asks for the
+// sign.)
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
 }
-
-// Hot-path variant for the common case of a single multiplier (ScaleMul::c2 == 0).
-__device__ __forceinline__ void dequant4_one_mul(uint32_t w, uint32_t c1, uint32_t& lo,
-                                                 uint32_t& hi) {
-  const uint32_t t0 = __byte_perm(w, 0u, 0x1404);     // [0, b0, 0, b1]
-  const uint32_t t1 = __byte_perm(w, 0u, 0x3424);     // [0, b2, 0, b3]
-  lo = bf16x2_mul((t0 & 0x80008000u) | ((t0 >> 4) & 0x07F007F0u), c1);
-  hi = bf16x2_mul((t1 & 0x80008000u) | ((t1 >> 4) & 0x07F007F0u), c1);
+struct ScalePair { uint32_t c1, c2; };               // packed BF16 factors
+__device__ __forceinline__ ScalePair scale_pair(uint32_t s) {
+  const uint32_t e1 = min(s + 120u, 247u);
+  return ScalePair{e1 * 0x00800080u, (s + 247u - e1) * 0x00800080u};
+}
+__device__ __forceinline__ void dequant4(uint32_t w, const ScalePair& c, uint32_t& lo, uint32_t& hi) {
+  const uint32_t t0 = prmt(w, 0u, 0x9180u);           // [b0, sign(b0), b1, sign(b1)]
+  const uint32_t t1 = prmt(w, 0u, 0xB3A2u);           // [b2, sign(b2), b3, sign(b3)]
+  lo = bf16x2_mul(bf16x2_mul((t0 << 4) & 0x87F087F0u, c.c1), c.c2);
+  hi = bf16x2_mul(bf16x2_mul((t1 << 4) & 0x87F087F0u, c.c1), c.c2);
 }
 
 // The same through fp32 arithmetic (no dependence on packed-BF16 subnormal
-// handling); kept as a cross-check of dequant4_fast.
+// handling); kept as a cross-check of dequant4.
 __device__ __forceinline__ void dequant4_f32(uint32_t w, uint32_t s, uint32_t& lo, uint32_t& hi) {
   float sc = ue8m0_scale_f32(s);
   __nv_bfloat162 a = __floats2bfloat162_rn(__fmul_rn(e4m3_to_f32(w & 0xffu), sc),

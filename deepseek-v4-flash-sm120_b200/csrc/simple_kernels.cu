@@ -262,7 +262,6 @@ kv_store_kernel(Dsv4StoreArgs a, const int32_t* slots32) {
   using T = KvTraits<FMT>;
   constexpr int PER_LANE = 16;                      // 32 lanes x 16 = 512 >= D_NOPE
   constexpr int LANES_PER_TILE = T::TILE / PER_LANE;
-  grid_launch_dependents();                         // the next kernel may be placed at once
   grid_dependency_wait();                           // the rows may come from the kernel before
   const int lane = threadIdx.x & 31;
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -364,10 +363,10 @@ gather_dequant_kernel(const uint8_t* kv, int64_t stride, int page_block, int n_t
     const uint32_t s = scl[lane * 16 / T::TILE];
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
     uint32_t o[8];
-    const ScaleMul mul = make_scale_mul(s);
+    const ScalePair mul = scale_pair(s);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      if (method == 0) dequant4_fast(w[i], mul, o[2 * i], o[2 * i + 1]);
+      if (method == 0) dequant4(w[i], mul, o[2 * i], o[2 * i + 1]);
       else dequant4_f32(w[i], s, o[2 * i], o[2 * i + 1]);
     }
     dst[lane * 2] = make_uint4(o[0], o[1], o[2], o[3]);

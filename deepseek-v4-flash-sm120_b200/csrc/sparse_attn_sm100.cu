@@ -378,34 +378,6 @@ __device__ __forceinline__ void load_line(uint4& d, const uint8_t* row, const Ge
     d = ldg16(row + 16 * piece + 128 * LINE);
 }
 
-// e4m3 -> BF16 with the block scale.  The byte, sign-extended to 16 bits and shifted left by
-// four, has the e4m3 magnitude bits where a BF16 word reads them as value * 2^-120 (normals
-// and subnormals alike) and the sign in bit 15.  Two packed multiplies then rescale and apply
-// the UE8M0 scale 2^(s-127) for EVERY scale byte, each of them exact (the value has at most
-// four significant bits) unless the result leaves the BF16 range, where the single rounding
-// is the same as that of an fp32 product rounded to BF16:
-//   s <= 127:  c1 = 2^(s-7),  c2 = 1;       s > 127:  c1 = 2^120 (giving the e4m3 value itself),
-//   c2 = 2^(s-127).
-// Branch-free and on the FMA pipe, which this kernel leaves idle; the integer pipe is the
-// busy one.  (prmt through inline PTX: __byte_perm drops the selector bit that asks for the
-// sign.)
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-  uint32_t d;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-  return d;
-}
-struct ScalePair { uint32_t c1, c2; };               // packed BF16 factors
-__device__ __forceinline__ ScalePair scale_pair(uint32_t s) {
-  const uint32_t e1 = min(s + 120u, 247u);
-  return ScalePair{e1 * 0x00800080u, (s + 247u - e1) * 0x00800080u};
-}
-__device__ __forceinline__ void dequant4(uint32_t w, const ScalePair& c, uint32_t& lo, uint32_t& hi) {
-  const uint32_t t0 = prmt(w, 0u, 0x9180u);           // [b0, sign(b0), b1, sign(b1)]
-  const uint32_t t1 = prmt(w, 0u, 0xB3A2u);           // [b2, sign(b2), b3, sign(b3)]
-  lo = bf16x2_mul(bf16x2_mul((t0 << 4) & 0x87F087F0u, c.c1), c.c2);
-  hi = bf16x2_mul(bf16x2_mul((t1 << 4) & 0x87F087F0u, c.c1), c.c2);
-}
-
 // Scale byte that applies to this lane's FP8 chunk of line LINE.
 template <int FMT, int LINE>
 __device__ __forceinline__ uint32_t scale_byte_of(const ScaleWords<FMT>& sw, int piece) {

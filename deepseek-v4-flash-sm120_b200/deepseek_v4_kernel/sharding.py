@@ -5,8 +5,8 @@ Three ways the path shards, none of which needs a collective inside the kernels:
     its own requests' pages (request-parallel, no communication);
   * decode by heads (tensor-parallel style): h_q / tp heads per rank over a
     replicated cache, followed by ONE all-gather of the per-head outputs;
-  * prefill by query blocks, balanced by the number of (query, key) pairs a
-    causal top-k gives each query rather than by row count.
+  * prefill by query blocks, balanced by the modelled time of each query row
+    (tiles of its causal top-k list plus a fixed cost per row) rather than by row count.
 The reference has none of this in-tree: SGLang supplies tensor parallelism and
 the kernel just sees a smaller h_q (its launch script sets
 --tensor-parallel-size 4).
@@ -39,14 +39,27 @@ def causal_pairs(s_q: int, topk: int, row0: int = 0) -> torch.Tensor:
     return torch.clamp(rows + 1, max=topk)
 
 
+TILE_ROWS = 128               # index entries the attention kernel handles per tile
+ROW_FIXED_TILES = 1.5         # set-up and epilogue of one query row, in tile times (measured)
+
+
+def row_cost(pairs: torch.Tensor) -> torch.Tensor:
+    """Modelled time of a prefill query row in tile units: the kernel walks a row's list in
+    tiles of 128 entries (a partly filled tile costs a whole one) and pays a fixed set-up and
+    epilogue per row, so short rows are dearer than their pair count says."""
+    tiles = (pairs + TILE_ROWS - 1) // TILE_ROWS
+    return tiles.to(torch.float64) + ROW_FIXED_TILES
+
+
 def balanced_query_blocks(s_q: int, topk: int, world: int) -> List[Tuple[int, int]]:
-    """Contiguous [begin, end) query blocks with near-equal pair counts."""
-    csum = torch.cumsum(causal_pairs(s_q, topk), 0)
-    total = int(csum[-1])
+    """Contiguous [begin, end) query blocks of near-equal modelled time (`row_cost` of the
+    causal pair counts)."""
+    csum = torch.cumsum(row_cost(causal_pairs(s_q, topk)), 0)
+    total = float(csum[-1])
     bounds = [0]
     for r in range(1, world):
-        target = total * r // world
-        bounds.append(int(torch.searchsorted(csum, torch.tensor(target), right=False)))
+        target = torch.tensor(total * r / world, dtype=torch.float64)
+        bounds.append(int(torch.searchsorted(csum, target, right=False)))
     bounds.append(s_q)
     return [(bounds[r], max(bounds[r], bounds[r + 1])) for r in range(world)]
 

@@ -301,14 +301,21 @@ typedef struct Dsv4StoreRowsArgs {
 
 int dsv4_kv_store_rows(const Dsv4StoreRowsArgs* args, void* cuda_stream);
 
-/* ---------------------------------------------------------------------------
- * Gather + dequantise only (checks that row selection and FP8 -> BF16 are
- * bit-exact): rows[i] = dequantised d_qk BF16 values of token indices[i], or
- * zeros for an index outside [0, num_blocks * page_block_size).  Uses the same
- * device routine as the decode kernel when method == 0 (packed-BF16 multiply);
- * method == 1 converts through fp32 instead (reference: load_kv_chunk,
- * csrc/sm120/decode/sparse_decode_kernel.cuh:101-167).
- * ------------------------------------------------------------------------- */
+/* ===========================================================================
+ * TEST HOOKS.  The three entries marked "test hook" below (dsv4_gather_dequant,
+ * dsv4_debug_set_timeline, dsv4_umma_selftest) exist for the test-suite and for
+ * profiling; a serving integration binds none of them.
+ * ===========================================================================
+ *
+ * Test hook.  Gather + dequantise only: rows[i] = dequantised d_qk BF16 values of
+ * token indices[i], or zeros for an index outside [0, num_blocks * page_block_size).
+ * method == 0 converts with the device function the attention kernel converts with
+ * (dequant4 in csrc/dsv4_common.cuh: two packed-BF16 multiplies), but stores the rows
+ * linearly, so it pins the conversion and the page addressing, not the kernel's
+ * shared-memory arrangement; the kernel's own path is pinned by decodes whose lists
+ * hold a single entry (the output must equal the value row).  method == 1 converts
+ * through fp32 instead (reference: load_kv_chunk,
+ * csrc/sm120/decode/sparse_decode_kernel.cuh:101-167).                                 */
 int dsv4_gather_dequant(const void* kv, int64_t stride_kv_block, int32_t kv_format,
                         int32_t num_blocks, int32_t page_block_size,
                         const int32_t* indices, int32_t n, void* rows_bf16,
@@ -325,7 +332,7 @@ int dsv4_device_info(int device, int* major, int* minor, int* num_sms);
  * loop need not call it; the tests do after every launch.                             */
 int dsv4_device_status(int32_t* status_out, int reset);
 
-/* Debug aid: give the attention kernels a device buffer of at least
+/* Test hook / debug aid: give the attention kernels a device buffer of at least
  * 1024 + 4 * (CTAs of the largest launch) int64.  CTA (0,0,0) of every later launch
  * writes SM cycle-counter stamps of its pipeline stages into the first 1024 slots and
  * every CTA four global-timer stamps (start, set-up done, last product done, end)
@@ -338,7 +345,7 @@ const char* dsv4_strerror(int status);
 const char* dsv4_last_cuda_error(void);
 int dsv4_abi_version(void);
 
-/* Tensor-core self-test used by the test-suite: one 128 x n x k BF16 product
+/* Test hook.  Tensor-core self-test: one 128 x n x k BF16 product
  * through tcgen05.mma with the shared-memory operand arrangement the attention
  * kernel uses (mode 0: both operands K-major; mode 1: A and B MN-major).
  * a, b, d are device pointers (BF16, BF16, fp32 row-major [128, n]).                   */
