@@ -709,11 +709,14 @@ sm100_attn_kernel(const AttnParams p) {
   grid_dependency_wait();          // inputs may come from the kernel before this one in the stream
   if (tid == 0) stamp(p, 0);
   if (tid == 0) stamp_cta(p, 0);
-  const int req = blockIdx.x, hb = blockIdx.y, split = blockIdx.z;
+  const bool decode = p.mode == MODE_DECODE;
+  // Prefill walks its query rows last to first: with causal lists the late rows are the
+  // long ones, and the grid should end on short rows, not on a wave of the longest.
+  const int req = decode ? blockIdx.x : gridDim.x - 1 - blockIdx.x;
+  const int hb = blockIdx.y, split = blockIdx.z;
   const int head0 = hb * NH;
   const int heads_here = min(NH, p.h_q - head0);
   const int bi = req / p.s_q, si = req % p.s_q;
-  const bool decode = p.mode == MODE_DECODE;
   const bool mask_invalid = !decode || (p.flags & DSV4_FLAG_MASK_INVALID);
   const bool split_out = p.n_splits > 1;
   const bool want_ml = p.max_logits != nullptr;
