@@ -424,40 +424,49 @@ __device__ __forceinline__ void store_line(const uint4& v, uint32_t sK, int row,
 // ---------------------------------------------------------------------------
 // Merging the splits of one request inside a thread-block cluster.
 // The `cs` CTAs of a cluster (consecutive splits, cluster dimension z) finish with
-// un-normalised O^T in TMEM, denominators l[h] and reference maxima m[h].  Each CTA
-//   1. copies its O^T, as it is, into its own shared memory as [head][d] fp32 (NH x 2 KB in
-//      the K tile region, which its own last product has released) and publishes (l, m);
-//   2. meets the others at a cluster barrier;
-//   3. reads every CTA's (l, m) through distributed shared memory and derives, per head,
-//      the weights 2^(m_s - M) / L of all sources (times the sink factor when this
-//      cluster holds all splits of the request);
-//   4. pulls slice r = its rank (d in [r, r+1) * 512 / cs) of every source with 16-byte
-//      ld.shared::cluster loads, sums in rank order and writes either the final BF16
-//      output or one normalised fp32 partial per cluster;
-//   5. meets the others again, so that no CTA retires while its memory is still read.
+// un-normalised O^T in TMEM, denominators l[h] and reference maxima m[h].  CTA r owns
+// slice r of the output (d in [r, r+1) * 512 / cs).  Each CTA
+//   1. meets the others at a cluster barrier (it arrives as soon as its own last product has
+//      retired and waits only here, after its local reductions): from here on every CTA's K
+//      tile region and small tables may be written by its peers;
+//   2. PUSHES: its (l, m) into every CTA's tables, and each 128-row slice of its O^T,
+//      straight from TMEM, into the staging area of the CTA that owns those d
+//      ([source][head][d] fp32 in the K tile region; st.shared::cluster, which does not
+//      wait for an answer the way a remote load does);
+//   3. meets the others again (release / acquire: the pushes are visible);
+//   4. derives, per head, the weights 2^(m_s - M) / L of all sources (times the sink
+//      factor when this cluster holds all splits of the request) from its own tables;
+//   5. sums its slice over the sources, in rank order, out of its own shared memory and
+//      writes either the final BF16 output or one normalised fp32 partial per cluster.
+// After step 3 no CTA touches another's memory, so none has to outlive the others.
 // Partial traffic to L2 and the combine kernel's input shrink by the cluster size, and
 // with n_splits == cs there is no combine launch at all.  An empty split (no tile) takes
-// part with l = 0, m = "none" (weight 0; its memory is not read); a CTA whose bounded wait
-// gave up still walks every barrier (its peers must not be left waiting) and only drops
-// its own stores.
+// part with l = 0, m = "none" (weight 0) and stages zeros; a CTA
+// whose bounded wait gave up still walks every barrier (its peers must not be left
+// waiting) and only drops its own stores.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
   return r;
 }
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  cluster_arrive();
+  cluster_wait();
 }
 __device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
-  return v;
+__device__ __forceinline__ void st_cluster_b32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
 // Everything the merge needs, by value (the kernel's parameter block must not have its
@@ -470,11 +479,22 @@ struct MergeOut {
   float* o_accum;
   __nv_bfloat16* out;
   int64_t stride_o_b, stride_o_s, stride_o_h, stride_lse_b, stride_lse_s, stride_lse_h;
+  long long* prof;         // debug timeline buffer or null
 };
 __device__ __forceinline__ MergeOut merge_out_of(const AttnParams& p) {
   return MergeOut{p.cluster, p.n_splits, p.mode, p.sink, p.lse, p.lse_accum, p.o_accum, p.out,
                   p.stride_o_b, p.stride_o_s, p.stride_o_h, p.stride_lse_b, p.stride_lse_s,
-                  p.stride_lse_h};
+                  p.stride_lse_h, p.prof};
+}
+constexpr int PROF_MERGE0 = 990;       // five stamps of the cluster merge (CTA (0,0,0), thread 0)
+__device__ __forceinline__ void stamp_merge(const MergeOut& p, int k) {
+#ifdef DSV4_TIMELINE
+  if (p.prof != nullptr && threadIdx.x == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0)
+    p.prof[PROF_MERGE0 + k] = clock64();
+#else
+  (void)p;
+  (void)k;
+#endif
 }
 struct MergeCtx {
   uint32_t stage;          // shared address of the staging area (the K tile region)
@@ -484,108 +504,116 @@ struct MergeCtx {
   bool empty;              // this split had no tile: no TMEM, contributes zeros
 };
 
-// Step (4) of the merge for a cluster of CS CTAs: thread = 4 consecutive d of one head; the
-// loads of BATCH items from all CS sources go out before the first is used (a remote load
-// takes on the order of a microsecond).
-template <int CS, int BATCH>
-__device__ __forceinline__ void pull_slices(const MergeOut& p, const Ctrl& ctrl, const MergeCtx& c,
-                                            float* const (&wtab)[4], uint32_t rank, bool final_out) {
-  constexpr int DL = D_V / CS, QUADS = DL / 4;
+// Step 5 of the merge for a cluster of CS CTAs: an item is 8 consecutive d of one head
+// (two 16-byte loads per source, one 16-byte store of BF16); staging area
+// [source][NH heads][512 / CS] fp32 in this CTA's own memory.  Kept lean: the epilogue is
+// bound by instruction issue (16 warps, every instruction counts 512 times).
+template <int NH, int CS>
+__device__ __forceinline__ void sum_slices(const MergeOut& p, const MergeCtx& c, const float* wtab,
+                                           uint32_t rank, bool final_out) {
+  constexpr int DL = D_V / CS, OCTS = DL / 8;
   const int tid = threadIdx.x;
-  const int n_items = c.heads_here * QUADS;
+  const int n_items = c.heads_here * OCTS;
   __nv_bfloat16* out_base = p.out + c.bi * p.stride_o_b + c.si * p.stride_o_s + c.head0 * p.stride_o_h;
-  for (int item0 = tid < WORKERS ? tid : n_items; item0 < n_items; item0 += BATCH * WORKERS) {
-    float4 v[BATCH][CS];
+#pragma unroll 2
+  for (int item = tid < WORKERS ? tid : n_items; item < n_items; item += WORKERS) {
+    const int h = item / OCTS, o = item - h * OCTS;
+    float acc[8];
 #pragma unroll
-    for (int k = 0; k < BATCH; ++k) {
-      const int item = item0 + k * WORKERS;
-      const int h = item / QUADS, q = item - h * QUADS;
-      const uint32_t a_loc = c.stage + (h * D_V + rank * DL + 4 * q) * 4;
+    for (int r = 0; r < CS; ++r) {                       // rank order: reproducible sums
+      const uint32_t a = c.stage + ((r * NH + h) * DL + 8 * o) * 4;
+      float v[8];
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "r"(a));
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]) : "r"(a + 16));
+      const float w = wtab[r * MAX_HEADS + h];
 #pragma unroll
-      for (int r = 0; r < CS; ++r) {
-        v[k][r] = make_float4(0.f, 0.f, 0.f, 0.f);
-        // weight 0: an empty split, whose memory holds nothing
-        if (item < n_items && wtab[r][h] != 0.f) {
-          if (r == static_cast<int>(rank)) {             // this CTA's own copy: plain shared load
-            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                         : "=f"(v[k][r].x), "=f"(v[k][r].y), "=f"(v[k][r].z), "=f"(v[k][r].w) : "r"(a_loc));
-          } else {
-            const uint32_t a = map_to_rank(a_loc, r);
-            asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                         : "=f"(v[k][r].x), "=f"(v[k][r].y), "=f"(v[k][r].z), "=f"(v[k][r].w) : "r"(a));
-          }
-        }
-      }
+      for (int i = 0; i < 8; ++i) acc[i] = r == 0 ? w * v[i] : fmaf(w, v[i], acc[i]);
     }
+    const int d0 = rank * DL + 8 * o;
+    if (final_out) {
+      uint32_t w4[4];
 #pragma unroll
-    for (int k = 0; k < BATCH; ++k) {
-      const int item = item0 + k * WORKERS;
-      if (item >= n_items || ctrl.fail) continue;
-      const int h = item / QUADS, q = item - h * QUADS;
-      const int d0 = rank * DL + 4 * q;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-      for (int r = 0; r < CS; ++r) {                     // rank order: reproducible sums
-        const float w = wtab[r][h];
-        acc.x = fmaf(w, v[k][r].x, acc.x);
-        acc.y = fmaf(w, v[k][r].y, acc.y);
-        acc.z = fmaf(w, v[k][r].z, acc.z);
-        acc.w = fmaf(w, v[k][r].w, acc.w);
+      for (int i = 0; i < 4; ++i) {
+        __nv_bfloat162 t = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+        w4[i] = *reinterpret_cast<uint32_t*>(&t);
       }
-      if (final_out) {
-        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
-        *reinterpret_cast<uint2*>(out_base + h * p.stride_o_h + d0) =
-            make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-      } else {
-        *reinterpret_cast<float4*>(p.o_accum + (c.acc_slot0 + h) * D_V + d0) = acc;
-      }
+      *reinterpret_cast<uint4*>(out_base + h * p.stride_o_h + d0) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+    } else {
+      float4* dst = reinterpret_cast<float4*>(p.o_accum + (c.acc_slot0 + h) * D_V + d0);
+      dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
   }
 }
 
-// `m_own` is in log2-scaled units, NEG_HUGE or -inf when the split saw nothing.
+// `m_own` is in log2-scaled units, NEG_HUGE or -inf when the split saw nothing.  Called by
+// the 512 workers (the MMA warpgroup mirrors the barriers), or by the whole CTA when the
+// split is empty.
 template <int NH>
 __device__ __noinline__ void cluster_merge(const MergeOut p, Ctrl& ctrl, const MergeCtx c,
                                            float l_own, float m_own) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int cs = p.cluster;                              // 2 or 4
+  const int dl = D_V / cs;
   const uint32_t rank = cluster_rank();
   const bool final_out = p.n_splits == cs;
 
-  // (1) own O^T -> own shared memory [head][d]; thread = one d (TMEM lane), 16 heads per load
+  cluster_wait();                                        // (1): the caller has arrived already
+  stamp_merge(p, 0);
+
+  // (2) tables: wred[source] = l, wmax[source] = m (both idle by now, in every CTA)
   if (tid < MAX_HEADS) {
-    ctrl.wred[0][tid] = l_own;
-    ctrl.wred[1][tid] = (m_own <= NEG_HUGE) ? -INFINITY : m_own;
+    const uint32_t a_l = smem_u32(&ctrl.wred[rank][tid]), a_m = smem_u32(&ctrl.wmax[rank][tid]);
+    const float mv = (m_own <= NEG_HUGE) ? -INFINITY : m_own;
+    for (int r = 0; r < cs; ++r) {
+      st_cluster_b32(map_to_rank(a_l, r), __float_as_uint(l_own));
+      st_cluster_b32(map_to_rank(a_m, r), __float_as_uint(mv));
+    }
   }
-  if (!c.empty) {
+  // O^T: thread = one d (TMEM lane), 16 heads per load; a warp's 32 d go to one owner,
+  // 128 contiguous bytes per store.  An empty split stages zeros (its weight is zero, and
+  // zero times whatever the memory held before need not be zero).
+  if (tid < WORKERS) {
     const int m = warp >> 2, lg = warp & 3;
     const int d = m * 128 + lg * 32 + lane;
+    const uint32_t owner = static_cast<uint32_t>(d / dl);
+    const uint32_t local = c.stage + ((rank * NH) * dl + (d - owner * dl)) * 4;
+    const uint32_t dst = owner == rank ? local : map_to_rank(local, owner);
 #pragma unroll 1
     for (int c4 = 0; c4 < NH / 16; ++c4) {
       uint32_t o[16];
-      tmem_ld16(c.tmem_o + m * O_SLICE_COLS + c4 * 16, o);
-      tmem_ld_wait();
+      if (!c.empty) {
+        tmem_ld16(c.tmem_o + m * O_SLICE_COLS + c4 * 16, o);
+        tmem_ld_wait();
+      } else {
 #pragma unroll
-      for (int i = 0; i < 16; ++i)
-        asm volatile("st.shared.b32 [%0], %1;" ::"r"(c.stage + ((c4 * 16 + i) * D_V + d) * 4), "r"(o[i]) : "memory");
+        for (int i = 0; i < 16; ++i) o[i] = 0u;
+      }
+      if (owner == rank) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst + (c4 * 16 + i) * dl * 4), "r"(o[i]) : "memory");
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) st_cluster_b32(dst + (c4 * 16 + i) * dl * 4, o[i]);
+      }
     }
   }
-  cluster_sync_all();                                    // (2)
+  stamp_merge(p, 1);
+  cluster_sync_all();                                    // (3)
+  stamp_merge(p, 2);
 
-  // (3) weights of all sources for head tid.  The table (4 sources x 64 heads) reuses arrays
-  // that are idle by now; wred[0] and wred[1] stay untouched, the peers are reading them.
-  float* wtab[4] = {ctrl.alpha, ctrl.wred[2], ctrl.wred[3], ctrl.aux};
+  // (4) weights of all sources for head tid; the table (4 sources x 64 heads) lives in the
+  // row table of the tile loop, which is idle by now
+  float* wtab = reinterpret_cast<float*>(&ctrl.rows[0][0][0]);
   if (tid < MAX_HEADS) {
-    const uint32_t a_l = smem_u32(&ctrl.wred[0][tid]), a_m = smem_u32(&ctrl.wred[1][tid]);
     float ms[4], ls[4];
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      ms[r] = -INFINITY;
-      ls[r] = 0.f;
-      if (r < cs) {
-        ms[r] = ld_cluster_f32(map_to_rank(a_m, r));
-        ls[r] = ld_cluster_f32(map_to_rank(a_l, r));
-      }
+      ms[r] = r < cs ? ctrl.wmax[r][tid] : -INFINITY;
+      ls[r] = r < cs ? ctrl.wred[r][tid] : 0.f;
     }
     const float big = fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3]));
     float w[4], total = 0.f;
@@ -609,14 +637,17 @@ __device__ __noinline__ void cluster_merge(const MergeOut p, Ctrl& ctrl, const M
         p.lse_accum[c.acc_slot0 + tid] = none ? -INFINITY : logf(total) + big * LN2;
     }
 #pragma unroll
-    for (int r = 0; r < 4; ++r) wtab[r][tid] = w[r] * f;
+    for (int r = 0; r < 4; ++r) wtab[r * MAX_HEADS + tid] = w[r] * f;
   }
   __syncthreads();
+  stamp_merge(p, 3);
 
-  // (4) pull this rank's slice of every source
-  if (cs == 2) pull_slices<2, 8>(p, ctrl, c, wtab, rank, final_out);
-  else pull_slices<4, 4>(p, ctrl, c, wtab, rank, final_out);
-  cluster_sync_all();                                    // (5) peers are done reading this CTA
+  // (5) this rank's slice, summed over the sources
+  if (!ctrl.fail) {
+    if (cs == 2) sum_slices<NH, 2>(p, c, wtab, rank, final_out);
+    else sum_slices<NH, 4>(p, c, wtab, rank, final_out);
+  }
+  stamp_merge(p, 4);
   // A CTA whose wait gave up makes the request's result visibly invalid.
   if (ctrl.fail && tid < c.heads_here) {
     if (final_out) p.lse[c.bi * p.stride_lse_b + c.si * p.stride_lse_s + (c.head0 + tid) * p.stride_lse_h] = NAN;
@@ -737,6 +768,7 @@ sm100_attn_kernel(const AttnParams p) {
   if (n_tiles == 0 && p.cluster > 1) {
     // Nothing to attend to, but the peers of the cluster count on this CTA at their barriers.
     if (tid == 0) ctrl.fail = 0;
+    cluster_arrive();
     __syncthreads();
     MergeCtx mc{sK, 0u, heads_here, head0, bi, si, acc_slot0, true};
     cluster_merge<NH>(merge_out_of(p), ctrl, mc, 0.f, -INFINITY);
@@ -860,8 +892,8 @@ sm100_attn_kernel(const AttnParams p) {
     __syncthreads();
     if (p.cluster > 1) {
       cluster_sync_all();
-      __syncthreads();
       cluster_sync_all();
+      __syncthreads();
     } else {
       __syncthreads();
     }
@@ -1208,6 +1240,8 @@ sm100_attn_kernel(const AttnParams p) {
   // ---- final denominators and output factors ---------------------------------------
   if (ok && !mbar_wait(bar_o_done, 0)) { atomicExch(&g_attn_error, ERR_ODONE); ok = false; }
   tc_fence_after_sync();
+  // This thread is done with the K tile: tell the cluster now, wait for it in the merge.
+  if (p.cluster > 1) cluster_arrive();
   if (tid == 0) stamp(p, 3);
   if (tid == 0) stamp_cta(p, 2);
   if (!ok) ctrl.fail = 1;
