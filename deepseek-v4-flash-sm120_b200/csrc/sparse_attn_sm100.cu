@@ -812,6 +812,23 @@ sm100_attn_kernel(const AttnParams p) {
     // It keeps 32 registers per thread and runs no code in common with the workers from here
     // on: only the CTA-wide (and cluster-wide) barriers, which it meets in the same order.
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(ISSUER_REGS));
+    // Its part of the set-up, off the workers' critical path: the barriers and TMEM (the warp
+    // next to the issuing one allocates and, at the end, frees it).
+    if (tid == WORKERS) {
+      for (int i = 0; i < 5; ++i) mbar_init(bar_blk_full0 + 8 * i, WORKER_WARPS);
+      for (int i = 0; i < 4; ++i) mbar_init(bar_slice_free0 + 8 * i, 1);
+      mbar_init(bar_s_full, 1);
+      mbar_init(bar_p_full, WORKER_WARPS);
+      mbar_init(bar_o_done, 1);
+      ctrl.resc = 0;
+      ctrl.fail = 0;
+      mbar_init_fence();
+    }
+    if (warp == ISSUE_WARP + 1) {
+      tmem_alloc(smem_u32(&ctrl.tmem), TMEM_COLS);
+      tmem_relinquish();
+    }
+    tc_fence_before_sync();
     __syncthreads();                 // set-up done: barriers initialised, TMEM allocated, Q stored
     tc_fence_after_sync();
     if (warp == ISSUE_WARP) {
@@ -899,6 +916,8 @@ sm100_attn_kernel(const AttnParams p) {
     }
     tc_fence_before_sync();
     __syncthreads();
+    tc_fence_after_sync();
+    if (warp == ISSUE_WARP + 1) tmem_dealloc(ctrl.tmem, TMEM_COLS);
     return;
   }
 
@@ -929,48 +948,29 @@ sm100_attn_kernel(const AttnParams p) {
     *reinterpret_cast<ulonglong2*>(&ctrl.rows[tile & 1][tid][0]) =
         make_ulonglong2(reinterpret_cast<unsigned long long>(r), reinterpret_cast<unsigned long long>(scl));
   };
-  int e_pref = -1;
+  // (a) The list entries go first: the tile-0 rows of this thread, the row-table entry of
+  // the first tile the loop requests and of the one after, the row that decides masking.
+  // Everything below that does not need them is issued behind their latency.
+  int e0[2] = {-1, -1};
+  if constexpr (S::PAGED) {
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) e0[hh] = list_index<EXTRA>(lv, lv.begin + geo.row(hh));
+  }
+  constexpr int FIRST_TABLE_TILE = LOAD_AHEAD - 1;       // the tile the first fill requests
+  int e_first = -1, e_pref = -1;
   if (tid < TILE) {
-    const int first = LOAD_AHEAD - 1;                    // the tile the first fill requests
-    if (first < n_tiles) write_rows(first, list_index<EXTRA>(lv, lv.begin + first * TILE + tid));
-    if (first + 1 < n_tiles) e_pref = list_index<EXTRA>(lv, lv.begin + (first + 1) * TILE + tid);
+    if (FIRST_TABLE_TILE < n_tiles) e_first = list_index<EXTRA>(lv, lv.begin + FIRST_TABLE_TILE * TILE + tid);
+    if (FIRST_TABLE_TILE + 1 < n_tiles)
+      e_pref = list_index<EXTRA>(lv, lv.begin + (FIRST_TABLE_TILE + 1) * TILE + tid);
   }
   // this thread's own tile row: its list entry decides masking when invalid entries are masked
   int ridx = 0, ridx_next = 0;
   if (mask_invalid) ridx = list_index<EXTRA>(lv, lv.begin + row);
+  if (tid == 0) stamp(p, 971);
 
-  // Q[head][d] -> blocks [d/64][head][64], 128-byte swizzle; absent heads are zero.
-  const __nv_bfloat16* qrow0 = p.q + bi * p.stride_q_b + si * p.stride_q_s + head0 * p.stride_q_h;
-  constexpr int Q_CHUNKS = NH * C::NB * 8;
-  constexpr int Q_BATCH = (Q_CHUNKS + WORKERS - 1) / WORKERS;     // all in flight at once
-  uint4 qv[Q_BATCH];
-#pragma unroll
-  for (int it = 0; it < Q_BATCH; ++it) {
-    const int i = tid + it * WORKERS;
-    const int h = i / (C::NB * 8), cc = i % (C::NB * 8);
-    qv[it] = make_uint4(0, 0, 0, 0);
-    if (i < Q_CHUNKS && h < heads_here)
-      qv[it] = ldg16(reinterpret_cast<const uint8_t*>(qrow0 + h * p.stride_q_h) + 16 * cc);
-  }
-  if (tid == 0) {
-    for (int i = 0; i < 5; ++i) mbar_init(bar_blk_full0 + 8 * i, WORKER_WARPS);
-    for (int i = 0; i < 4; ++i) mbar_init(bar_slice_free0 + 8 * i, 1);
-    mbar_init(bar_s_full, 1);
-    mbar_init(bar_p_full, WORKER_WARPS);
-    mbar_init(bar_o_done, 1);
-    ctrl.resc = 0;
-    ctrl.fail = 0;
-    mbar_init_fence();
-  }
-  if (tid < MAX_HEADS) {
-    ctrl.mref[tid] = NEG_HUGE;
-    ctrl.alpha[tid] = 1.f;
-  }
-  if (warp == 0) {
-    tmem_alloc(smem_u32(&ctrl.tmem), TMEM_COLS);
-    tmem_relinquish();
-  }
-  // First use of the list entries: the first tile's rows and scale bytes go in flight.
+  // (b) First use of the list entries: the first tile's rows and scale bytes go in flight,
+  // ahead of Q: they come from DRAM and are what the first product waits for, and the SM
+  // keeps only so many loads in flight.
   ScaleWords<FMT> sw_cur[2], sw_ld[2];
   const uint8_t* row_ld[2] = {nullptr, nullptr};
 #pragma unroll
@@ -984,13 +984,38 @@ sm100_attn_kernel(const AttnParams p) {
     for (int hh = 0; hh < 2; ++hh) {
       const int j = lv.begin + geo.row(hh);
       const uint8_t* scl;
-      const uint8_t* r0 = row_ptr<FMT>(cache_of<EXTRA>(p, lv, j), list_index<EXTRA>(lv, j), scl);
+      const uint8_t* r0 = row_ptr<FMT>(cache_of<EXTRA>(p, lv, j), e0[hh], scl);
       load_scale_words<FMT>(sw_cur[hh], scl);
       static_for<0, S::LINES>([&](auto lc) {
         load_line<FMT, DQK, decltype(lc)::value>(stage.d[hh][decltype(lc)::value], r0, geo);
       });
     }
   }
+  if (tid == 0) stamp(p, 972);
+
+  // (c) Q[head][d] -> blocks [d/64][head][64], 128-byte swizzle; absent heads are zero.
+  const __nv_bfloat16* qrow0 = p.q + bi * p.stride_q_b + si * p.stride_q_s + head0 * p.stride_q_h;
+  constexpr int Q_CHUNKS = NH * C::NB * 8;
+  constexpr int Q_BATCH = (Q_CHUNKS + WORKERS - 1) / WORKERS;     // all in flight at once
+  uint4 qv[Q_BATCH];
+#pragma unroll
+  for (int it = 0; it < Q_BATCH; ++it) {
+    const int i = tid + it * WORKERS;
+    const int h = i / (C::NB * 8), cc = i % (C::NB * 8);
+    qv[it] = make_uint4(0, 0, 0, 0);
+    if (i < Q_CHUNKS && h < heads_here)
+      qv[it] = ldg16(reinterpret_cast<const uint8_t*>(qrow0 + h * p.stride_q_h) + 16 * cc);
+  }
+  if (tid == 0) stamp(p, 974);
+
+  // (d) the row table of the first tile the loop requests; the softmax references
+  if (tid < TILE && FIRST_TABLE_TILE < n_tiles) write_rows(FIRST_TABLE_TILE, e_first);
+  if (tid < MAX_HEADS) {
+    ctrl.mref[tid] = NEG_HUGE;
+    ctrl.alpha[tid] = 1.f;
+  }
+  // (e) Q into shared memory (the barriers and the TMEM allocation are the fifth
+  // warpgroup's part of the set-up)
 #pragma unroll
   for (int it = 0; it < Q_BATCH; ++it) {
     const int i = tid + it * WORKERS;
@@ -999,6 +1024,7 @@ sm100_attn_kernel(const AttnParams p) {
       st_shared_v4(sQ + kb * C::QBLOCK_BYTES + h * 128 + ((ch ^ (h & 7)) << 4), qv[it].x, qv[it].y,
                    qv[it].z, qv[it].w);
   }
+  if (tid == 0) stamp(p, 975);
   fence_async_smem();
   tc_fence_before_sync();
   __syncthreads();
@@ -1318,7 +1344,6 @@ sm100_attn_kernel(const AttnParams p) {
   __syncthreads();
   if (tid == 0) stamp(p, 5);
   if (tid == 0) stamp_cta(p, 3);
-  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 // The dynamic shared-memory limit of a kernel is a per-device attribute: set once per
