@@ -111,6 +111,12 @@ __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src, u
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src),
                "r"(src_bytes) : "memory");
 }
+// One arrival on `bar` (counted among its expected arrivals) once every cp.async this thread
+// has issued so far has landed.  No thread waits for the copies; as CUTLASS's sm100 cp.async
+// pipelines do, the tensor core may read the bytes once the barrier phase completes.
+__device__ __forceinline__ void cp_async_mbar_arrive(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() {
   asm volatile("cp.async.commit_group;" ::: "memory");
 }

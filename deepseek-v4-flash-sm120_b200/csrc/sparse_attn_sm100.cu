@@ -815,7 +815,9 @@ sm100_attn_kernel(const AttnParams p) {
     // Its part of the set-up, off the workers' critical path: the barriers and TMEM (the warp
     // next to the issuing one allocates and, at the end, frees it).
     if (tid == WORKERS) {
-      for (int i = 0; i < 5; ++i) mbar_init(bar_blk_full0 + 8 * i, WORKER_WARPS);
+      // a group is published by the 16 worker warps, or (flat BF16 rows) by the completion of
+      // every worker thread's asynchronous copies
+      for (int i = 0; i < 5; ++i) mbar_init(bar_blk_full0 + 8 * i, C::PAGED ? WORKER_WARPS : WORKERS);
       for (int i = 0; i < 4; ++i) mbar_init(bar_slice_free0 + 8 * i, 1);
       mbar_init(bar_s_full, 1);
       mbar_init(bar_p_full, WORKER_WARPS);
@@ -1043,8 +1045,8 @@ sm100_attn_kernel(const AttnParams p) {
     // matched; the outputs are then suppressed.
     // Paged: the rows are in registers; each line is reloaded with the same line of tile
     // `ld_tile` as soon as it has been stored.  BF16: the rows of tile ld_tile == st_tile
-    // are copied with cp.async; group g is published once its copies have landed, which is
-    // checked after group g + 1 has been issued.
+    // are copied with cp.async, and group g publishes itself: each thread's arrival on the
+    // group's barrier is tied to the completion of its copies, so no thread waits for them.
     auto publish = [&](int g) {              // this warp's part of group g is in shared memory
       fence_async_smem();
       __syncwarp();
@@ -1091,15 +1093,8 @@ sm100_attn_kernel(const AttnParams p) {
               cp_async16(dst, src, row_ld[hh] != nullptr ? 16u : 0u);
             }
           });
-          cp_async_commit();
-          if constexpr (g > 0) {
-            cp_async_wait<1>();
-            publish(g - 1);
-          }
-          if constexpr (g == NG - 1) {
-            cp_async_wait<0>();
-            publish(g);
-          }
+          // every worker thread arrives on the group's barrier when its own copies land
+          cp_async_mbar_arrive(bar_blk_full0 + 8 * g);
         }
       });
     };
