@@ -927,9 +927,9 @@ sm100_attn_kernel(const AttnParams p) {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(WORKER_REGS));
 
   // ---- set-up ---------------------------------------------------------------------------
-  // Order matters for latency: the list entries are requested first, then Q (which depends
-  // on nothing), then, as the entries arrive, the first tile's rows and their scale bytes;
-  // Q is written to shared memory while the rows are in flight.
+  // Order matters for latency: the list entries are requested first, then, as they arrive,
+  // the first tile's rows and their scale bytes (DRAM: what the first product waits for),
+  // then Q; Q is written to shared memory while the rows are in flight.
   S stage;
   const Geo geo{warp >> 2, 4 * (warp & 3) + (lane & 1) + 2 * (lane >> 4),
                 ((lane >> 1) & 3) + 4 * ((lane >> 3) & 1), 2 * ((lane >> 1) & 3) + ((lane >> 3) & 1)};
