@@ -58,12 +58,14 @@ __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
 
 // e4m3 -> BF16 with the block scale.  The byte, sign-extended to 16 bits and shifted left by
 // four, has the e4m3 magnitude bits where a BF16 word reads them as value * 2^-120 (normals
-// and subnormals alike) and the sign in bit 15.  Two packed multiplies then rescale and apply
-// the UE8M0 scale 2^(s-127) for EVERY scale byte, each of them exact (the value has at most
-// four significant bits) unless the result leaves the BF16 range, where the single rounding
-// is the same as that of an fp32 product rounded to BF16:
-//   s <= 127:  c1 = 2^(s-7),  c2 = 1;       s > 127:  c1 = 2^120 (giving the e4m3 value itself),
-//   c2 = 2^(s-127).
+// and subnormals alike) and the sign in bit 15.  One packed multiply by c1 = 2^(s-7) then
+// rescales and applies the UE8M0 scale 2^(s-127); it is exact (the value has at most four
+// significant bits) unless the result leaves the BF16 range, where the single rounding is
+// the same as that of an fp32 product rounded to BF16.  2^(s-7) is a finite BF16 number for
+// scale bytes up to 134; beyond that c1 = 2^127 and a second multiply by c2 = 2^(s-134)
+// follows (c2 = 1 otherwise).  `two` says whether the second multiply is applied: callers
+// pass "c2 is not one", which the attention kernel evaluates once per tile and warp, so
+// that the common case costs one multiply per two values.
 // Branch-free and on the FMA pipe, which the attention kernel leaves idle; its integer pipe is the
 // busy one.  (prmt through inline PTX: __byte_perm drops the selector bit that asks for the
 // sign.)
@@ -72,16 +74,26 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
   return d;
 }
+constexpr uint32_t MAX_ONE_MULTIPLY_SCALE = 134;     // largest scale byte with c2 == 1
+constexpr uint32_t BF16X2_ONE = 0x3f803f80u;
 struct ScalePair { uint32_t c1, c2; };               // packed BF16 factors
 __device__ __forceinline__ ScalePair scale_pair(uint32_t s) {
-  const uint32_t e1 = min(s + 120u, 247u);
+  const uint32_t e1 = min(s + 120u, 254u);
   return ScalePair{e1 * 0x00800080u, (s + 247u - e1) * 0x00800080u};
 }
-__device__ __forceinline__ void dequant4(uint32_t w, const ScalePair& c, uint32_t& lo, uint32_t& hi) {
+// Does any of the four scale bytes in `w` need the second multiply?
+__device__ __forceinline__ bool needs_second_multiply(uint32_t w) {
+  return __vcmpgtu4(w, MAX_ONE_MULTIPLY_SCALE * 0x01010101u) != 0u;
+}
+__device__ __forceinline__ void dequant4(uint32_t w, const ScalePair& c, bool two, uint32_t& lo, uint32_t& hi) {
   const uint32_t t0 = prmt(w, 0u, 0x9180u);           // [b0, sign(b0), b1, sign(b1)]
   const uint32_t t1 = prmt(w, 0u, 0xB3A2u);           // [b2, sign(b2), b3, sign(b3)]
-  lo = bf16x2_mul(bf16x2_mul((t0 << 4) & 0x87F087F0u, c.c1), c.c2);
-  hi = bf16x2_mul(bf16x2_mul((t1 << 4) & 0x87F087F0u, c.c1), c.c2);
+  lo = bf16x2_mul((t0 << 4) & 0x87F087F0u, c.c1);
+  hi = bf16x2_mul((t1 << 4) & 0x87F087F0u, c.c1);
+  if (two) {
+    lo = bf16x2_mul(lo, c.c2);
+    hi = bf16x2_mul(hi, c.c2);
+  }
 }
 
 // The same through fp32 arithmetic (no dependence on packed-BF16 subnormal

@@ -366,7 +366,7 @@ gather_dequant_kernel(const uint8_t* kv, int64_t stride, int page_block, int n_t
     const ScalePair mul = scale_pair(s);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      if (method == 0) dequant4(w[i], mul, o[2 * i], o[2 * i + 1]);
+      if (method == 0) dequant4(w[i], mul, mul.c2 != BF16X2_ONE, o[2 * i], o[2 * i + 1]);
       else dequant4_f32(w[i], s, o[2 * i], o[2 * i + 1]);
     }
     dst[lane * 2] = make_uint4(o[0], o[1], o[2], o[3]);

@@ -391,7 +391,7 @@ __device__ __forceinline__ uint32_t scale_byte_of(const ScaleWords<FMT>& sw, int
 // Convert and store line LINE of the staged row `v` (tile row `row`).
 template <int FMT, int DQK, int LINE>
 __device__ __forceinline__ void store_line(const uint4& v, uint32_t sK, int row, const Geo& geo,
-                                           const ScaleWords<FMT>& sw) {
+                                           const ScaleWords<FMT>& sw, bool two) {
   using S = Stage<FMT, DQK>;
   constexpr int NB = DQK / 64;
   const int piece = S::copied_line(LINE) ? geo.piece_cp : geo.piece;
@@ -404,10 +404,14 @@ __device__ __forceinline__ void store_line(const uint4& v, uint32_t sK, int row,
       const ScalePair c = scale_pair(scale_byte_of<FMT, LINE>(sw, piece));
       const uint32_t a = rbase + (ci >> 2) * KBLOCK_BYTES + (((2 * (ci & 3)) ^ x) << 4);
       uint32_t o[8];
-      dequant4(v.x, c, o[0], o[1]);
-      dequant4(v.y, c, o[2], o[3]);
-      dequant4(v.z, c, o[4], o[5]);
-      dequant4(v.w, c, o[6], o[7]);
+      dequant4(v.x, c, false, o[0], o[1]);
+      dequant4(v.y, c, false, o[2], o[3]);
+      dequant4(v.z, c, false, o[4], o[5]);
+      dequant4(v.w, c, false, o[6], o[7]);
+      if (two) {                               // warp-uniform, and next to never taken
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = bf16x2_mul(o[i], c.c2);
+      }
       st_shared_v4(a, o[0], o[1], o[2], o[3]);
       st_shared_v4(a ^ 16, o[4], o[5], o[6], o[7]);             // the neighbouring chunk
     } else if (ci < S::CH) {
@@ -1053,6 +1057,18 @@ sm100_attn_kernel(const AttnParams p) {
       if (lane == 0) mbar_arrive(bar_blk_full0 + 8 * g);
     };
     auto fill = [&](int wait_tile, bool load_next) {
+      // Does any row this warp converts in this tile carry a scale byte beyond the reach of
+      // one multiply?  (Warp-uniform, so the second multiply is a branch, not a predicate.)
+      bool two = false;
+      if constexpr (S::PAGED) {
+        bool mine = false;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+#pragma unroll
+          for (int k = 0; k < ScaleWords<FMT>::N; ++k) mine |= needs_second_multiply(sw_cur[hh].w[k]);
+        }
+        two = __any_sync(0xffffffffu, mine);
+      }
       static_for<0, NG>([&](auto gc) {
         constexpr int g = decltype(gc)::value;
         constexpr int FREED_BY = g < 3 ? g : 3;
@@ -1067,7 +1083,7 @@ sm100_attn_kernel(const AttnParams p) {
             constexpr int line = decltype(lc)::value;
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
-              store_line<FMT, DQK, line>(stage.d[hh][line], sK, geo.row(hh), geo, sw_cur[hh]);
+              store_line<FMT, DQK, line>(stage.d[hh][line], sK, geo.row(hh), geo, sw_cur[hh], two);
             }
           });
           // the requests for the same lines of the tile after next go out before the proxy
