@@ -528,7 +528,8 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "us_per_call": e2e_us, "calls_timed": n_e2e,
                     "eager_single_stream_us_per_call": eager_us,
-                    "how": "ops.sparse_decode_fwd with host buffers: upload + operator + download "
+                    "how": "one e2e step is ONE call (the byte counts are per call): "
+                           "ops.sparse_decode_fwd with host buffers: upload + operator + download "
                            "captured per index set as a CUDA graph, steps round-robin over 3 streams; "
                            "eager_single_stream_us_per_call is one uncaptured call at a time "
                            "(upload, operator, download, synchronise), wall clock"},
